@@ -64,6 +64,7 @@ class KvLayout:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: keep every position
+    values: bool = True              # False: one pool of rows only (a layer whose values are part of its key rows)
 
 
 class GroupBook:

@@ -64,7 +64,7 @@ class Cache:
         for layout, m in zip(layouts, members):
             shape = (len(m), n_pages, layout.num_kv_heads, PAGE, layout.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device))
+            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device) if layout.values else None)
         self.engine_state = torch.zeros((max_slots, STATE_WORDS), dtype=torch.int64, device=device)
         self.layers = []
         for idx, (layout, state, cache_of) in enumerate(requests):
@@ -74,7 +74,8 @@ class Cache:
             src = cache_of if cache_of is not None else idx
             if src in owner_group:
                 g, j = owner_group[src]
-                self.layers.append(LayerCache(self.k_pools[g][j], self.v_pools[g][j], g, cache_of is None, st))
+                v_pool = self.v_pools[g][j] if self.v_pools[g] is not None else None
+                self.layers.append(LayerCache(self.k_pools[g][j], v_pool, g, cache_of is None, st))
             else:
                 self.layers.append(LayerCache(None, None, None, False, st))
 
@@ -97,4 +98,9 @@ class Cache:
 
     def bytes_per_token(self) -> int:
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(m) * l.num_kv_heads * l.head_dim * el for l, m in zip(self.layouts, self.members))
+        return sum((2 if l.values else 1) * len(m) * l.num_kv_heads * l.head_dim * el
+                   for l, m in zip(self.layouts, self.members))
+
+    def state_bytes(self) -> int:
+        """Bytes of the mixers' per-sequence states over all slots."""
+        return sum(l.state.numel() * l.state.element_size() for l in self.layers if l.state is not None)

@@ -100,6 +100,137 @@ class MoeFfnSpec:
 
 
 @dataclass(frozen=True)
+class ScaledRopeSpec:
+    """Split-half rotary encoding whose slow frequencies are interpolated (YaRN): with ``factor`` None the plain
+    frequencies theta^(-2i/d).  Else pair i keeps its frequency while i lies below the pair that makes ``fast``
+    turns within ``original`` positions, is divided by ``factor`` beyond the pair that makes ``slow`` turns, with
+    a linear ramp between; cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    rotary_dim: int
+    theta: float
+    factor: Optional[float] = None
+    original: Optional[float] = None
+    fast: Optional[float] = None
+    slow: Optional[float] = None
+    kind: str = "rope_split_half_scaled"
+
+
+@dataclass(frozen=True)
+class LatentAttentionNames:
+    """Tensor names of an attention layer with low-rank queries and a cached latent, after the spec's prefix."""
+    q_down: str = "dq"
+    q_norm: str = "dq.norm"
+    q_up: str = "uq"
+    kv_down: str = "dkv"
+    kv_norm: str = "dkv.norm"
+    k_up: str = "uk"
+    v_up: str = "uv"
+    o: str = "o"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose keys and values are up-projections of one cached latent per position plus one
+    rotated key part shared by the heads.  Per head: ``nope_dim`` unrotated and ``rot_dim`` rotated query/key
+    channels, ``value_dim`` value channels."""
+    hidden: int
+    num_heads: int
+    nope_dim: int
+    rot_dim: int
+    value_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float                     # multiplies the scores as given
+    window: Optional[int]            # None: every earlier key; W: the query and W-1 predecessors
+    keep_window: Optional[int]       # how far back the cache has to reach for every layer that reads it
+    eps: float                       # of the two latent norms
+    position: ScaledRopeSpec
+    own_kv: bool                     # False: the layer has no down-projection and reads another layer's cache
+    prefix: str
+    kind: str = "latent_attention"
+    names: LatentAttentionNames = LatentAttentionNames()
+
+
+@dataclass(frozen=True)
+class GatedRecurrenceNames:
+    """Tensor names of the two gated linear recurrences, after the spec's prefix."""
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    o: str = "o"
+    norm: str = "norm"
+    gate: str = "g"                  # output gate (decay form)
+    forget: str = "f"                # forget gate's projection (lower-bound form); its bias is forget + ".b"
+    lower: str = "lower"
+    receptance: str = "r"
+    decay_in: str = "w1"
+    decay_out: str = "w2"
+    decay_bias: str = "w0"
+    bonus: str = "u"
+    shift: str = "mu."               # + one of r, k, v, g, w
+
+
+@dataclass(frozen=True)
+class LowerBoundRecurrenceSpec:
+    """Linear attention whose forget gate f (bounded below per channel) also decides what is written:
+    S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T silu(q_t); per-head RMS norm with one weight vector
+    shared by the heads."""
+    hidden: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    eps: float
+    prefix: str
+    kind: str = "hgrn2"
+    names: GatedRecurrenceNames = GatedRecurrenceNames()
+
+
+@dataclass(frozen=True)
+class DecayBonusRecurrenceSpec:
+    """Time mixing with token shift, a data-dependent decay per key channel from a low-rank projection, and a
+    bonus for the current token: o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t, S_t = diag(w_t) S_(t-1) + k_t v_t^T;
+    per-head unit RMS, a weight per channel and a SiLU gate."""
+    hidden: int
+    num_heads: int
+    head_dim: int
+    decay_rank: int
+    eps: float
+    prefix: str
+    kind: str = "wkv"
+    names: GatedRecurrenceNames = GatedRecurrenceNames()
+
+
+@dataclass(frozen=True)
+class XieluFfnSpec:
+    """down(xIELU(up h)) with the activation's two learned numbers in one tensor."""
+    hidden: int
+    intermediate: int
+    prefix: str
+    kind: str = "xielu"
+    up: str = "up"
+    down: str = "down"
+    act: str = "act"
+
+
+@dataclass(frozen=True)
+class DepthMixBlockSpec:
+    """Pre-norm layer whose two results are scaled channel by channel (times ``residual_mult``) before they
+    join the residual stream, and whose successor gets a weighted sum of the embedding output and every
+    layer's result so far (``index`` counts the layers from 0; the weights tensor has index + 2 entries)."""
+    mixer: Any
+    ffn: Any                         # None: no feed-forward (and no second norm or scale)
+    mixer_norm: NormSpec
+    ffn_norm: Optional[NormSpec]
+    residual_mult: float
+    mixer_scale: str                 # tensor names
+    ffn_scale: Optional[str]
+    depth_weights: str
+    index: int
+    depth: int                       # layers of the model
+    hidden: int
+    kind: str = "prenorm_scaled_depthmix"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: which parts it has and how they are arranged."""
     mixer: Any                       # any spec object with a ``kind``

@@ -33,6 +33,8 @@ def config_from_dict(raw: dict):
     if raw.get("text_config") is not None:
         raise Unsupported("text_config", "multimodal configs nest the language model; only a flat decoder config runs")
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]              # configurations that name their one architecture as a string
     model_type = raw.get("model_type")
     if archs is not None and (not isinstance(archs, list) or not all(isinstance(a, str) for a in archs)):
         raise InvalidConfig("architectures must be a list of strings")

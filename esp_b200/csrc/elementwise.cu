@@ -52,14 +52,15 @@ ESP_API int esp_feed_tokens(int* ids, const int* picks, const int* src, int n, c
 
 // ---------------------------------------------------------------- add + RMSNorm
 // Row r works on source row s = rows ? rows[r] : r.
-//   v = x[s] + (y ? y[s] : 0);  if (write_x) x[s] = v;
+//   v = x[s] + (y ? y[s] * (yscale ? yscale : 1) : 0);  if (write_x) x[s] = v;      (yscale: one factor per channel)
 //   h[r] = v * (1 / sqrt(mean(v^2) + eps)) * gamma       (all in 32-bit)
 // ``h32`` (may be null) receives the same rows unrounded, for consumers that
 // must work from 32-bit values whatever the activation dtype (the router).
 // The sum of squares is taken per thread in index order and combined by a
 // fixed tree, so a row's result does not depend on the rest of the batch.
 template <typename TH>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma,
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ yscale,
+                                   const float* __restrict__ gamma,
                                    const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width,
                                    float eps, int write_x) {
     pdl_trigger();
@@ -73,7 +74,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = xr[i];
         if (yr) {
-            v += yr[i];
+            v += yscale ? yr[i] * yscale[i] : yr[i];
             if (write_x) xr[i] = v;
         }
         ss = fmaf(v, v, ss);
@@ -84,7 +85,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
     float* h32r = h32 ? h32 + (size_t)r * width : nullptr;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = xr[i];
-        if (yr && !write_x) v += yr[i];
+        if (yr && !write_x) v += yscale ? yr[i] * yscale[i] : yr[i];
         const float o = v * inv * gamma[i];
         hr[i] = from_f32<TH>(o);
         if (h32r) h32r[i] = o;
@@ -96,8 +97,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const float* __restric
 // The sum of squares is taken per thread in piece order and combined by the same fixed tree.
 template <typename TH>
 __global__ void __launch_bounds__(1024)
-add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma,
-                        const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width, float eps,
+add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ yscale,
+                        const float* __restrict__ gamma, const int* __restrict__ rows, TH* __restrict__ h, float* __restrict__ h32, int width, float eps,
                         int write_x) {
     pdl_trigger();
     pdl_wait();
@@ -115,7 +116,11 @@ add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, cons
         if (q < pieces) {
             v[i] = xr[q];
             if (yr) {
-                const float4 a = yr[q];
+                float4 a = yr[q];
+                if (yscale) {
+                    const float4 sc = reinterpret_cast<const float4*>(yscale)[q];
+                    a.x *= sc.x; a.y *= sc.y; a.z *= sc.z; a.w *= sc.w;
+                }
                 v[i].x += a.x; v[i].y += a.y; v[i].z += a.z; v[i].w += a.w;
                 if (write_x) xr[q] = v[i];
             }
@@ -140,7 +145,7 @@ add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, cons
     }
 }
 
-ESP_API int esp_add_rmsnorm(float* x, const float* y, const float* gamma, const int* rows, void* h, int h_is_bf16,
+ESP_API int esp_add_rmsnorm(float* x, const float* y, const float* yscale, const float* gamma, const int* rows, void* h, int h_is_bf16,
                             float* h32, int n_rows, int width, float eps, int write_x, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width % 4 == 0 && width <= 16384) {
@@ -150,16 +155,16 @@ ESP_API int esp_add_rmsnorm(float* x, const float* y, const float* gamma, const 
         // blocks, more rows in flight per SM.
         if (width / 4 <= 1024 && !(h_is_bf16 && n_rows >= 256)) threads = (width / 4 + 31) / 32 * 32;
         if (h_is_bf16)
-            esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_rows_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
+            esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_rows_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, y, yscale, gamma, rows, (bf16*)h, h32, width, eps, write_x);
         else
-            esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma, rows, (float*)h, h32, width, eps, write_x);
+            esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y, yscale, gamma, rows, (float*)h, h32, width, eps, write_x);
         return esp_launch_status();
     }
     const int threads = width >= 1024 ? 256 : 128;
     if (h_is_bf16)
-        esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
+        esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, y, yscale, gamma, rows, (bf16*)h, h32, width, eps, write_x);
     else
-        esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma, rows, (float*)h, h32, width, eps, write_x);
+        esp_launch_pdl(ESP_PDL_SMALL, add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y, yscale, gamma, rows, (float*)h, h32, width, eps, write_x);
     return esp_launch_status();
 }
 
@@ -305,5 +310,84 @@ ESP_API int esp_normal_fill(void* out, int out_is_bf16, long long count, unsigne
         normal_fill_kernel<bf16><<<(int)blocks, 256, 0, stream>>>((bf16*)out, count, key, mean, stddev);
     else
         normal_fill_kernel<float><<<(int)blocks, 256, 0, stream>>>((float*)out, count, key, mean, stddev);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- depth-weighted average of the layers' results
+// history: [slots_of_history, n_rows, width] float; entries 0 .. index hold the results X_0 .. X_index of the
+// embedding and the layers so far.  This call finishes layer ``index``:
+//   X_(index+1) = x + (y ? y * yscale : 0)        -> history[index + 1]
+//   x           = sum_(j = 0 .. index+1) weights[j] * X_j        (added in ascending j)
+__global__ void depth_mix_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ yscale,
+                                 float* __restrict__ history, const float* __restrict__ weights, int index,
+                                 long long count, int width) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        float v = x[i];
+        if (y) v += yscale ? y[i] * yscale[i % width] : y[i];
+        history[(size_t)(index + 1) * count + i] = v;
+        float acc = 0.f;
+        for (int j = 0; j <= index; j++) acc = fmaf(weights[j], history[(size_t)j * count + i], acc);
+        x[i] = fmaf(weights[index + 1], v, acc);
+    }
+}
+
+ESP_API int esp_depth_mix(float* x, const float* y, const float* yscale, float* history, const float* weights, int index,
+                          int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const long long count = (long long)n_rows * width;
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    esp_launch_pdl(ESP_PDL_SMALL, depth_mix_kernel, dim3((int)blocks), dim3(256), 0, stream, x, y, yscale, history, weights,
+                   index, count, width);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- xIELU
+// act = a_p z^2 + z / 2 (z > 0);  a_n (exp(z) - 1 - z) + z / 2 (z <= 0);  a_p = softplus(p), a_n = 1/2 + softplus(q),
+// p and q being the two learned numbers in ``pq``.
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+template <typename TO>
+__global__ void xielu_kernel(const float* __restrict__ z, const float* __restrict__ pq, TO* __restrict__ act, long long count) {
+    pdl_trigger();
+    pdl_wait();
+    const float ap = softplus_f(pq[0]), an = 0.5f + softplus_f(pq[1]);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
+        const float v = z[i];
+        const float r = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
+        act[i] = from_f32<TO>(r);
+    }
+}
+
+ESP_API int esp_xielu(const float* z, const float* pq, void* act, int act_is_bf16, long long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (act_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, xielu_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, z, pq, (bf16*)act, count);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, xielu_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, pq, (float*)act, count);
+    return esp_launch_status();
+}
+
+// out = tanh(in), for the small hidden layer of a data-dependent decay
+template <typename TO>
+__global__ void tanh_kernel(const float* __restrict__ z, TO* __restrict__ out, long long count) {
+    pdl_trigger();
+    pdl_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<TO>(tanhf(z[i]));
+}
+
+ESP_API int esp_tanh(const float* z, void* out, int out_is_bf16, long long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    long long blocks = (count + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (out_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, tanh_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, z, (bf16*)out, count);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, tanh_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, (float*)out, count);
     return esp_launch_status();
 }

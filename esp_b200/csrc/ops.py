@@ -23,7 +23,20 @@ _SIGNATURES = {
     "esp_embed_gather": [P, c_int, P, P, c_int, c_int, c_int, c_float, P, P],
     "esp_softcap": [P, c_longlong, c_float, P],
     "esp_feed_tokens": [P, P, P, c_int, P],
-    "esp_add_rmsnorm": [P, P, P, P, P, c_int, P, c_int, c_int, c_float, c_int, P],
+    "esp_add_rmsnorm": [P, P, P, P, P, P, c_int, P, c_int, c_int, c_float, c_int, P],
+    "esp_depth_mix": [P, P, P, P, P, c_int, c_int, c_int, P],
+    "esp_xielu": [P, P, P, c_int, c_longlong, P],
+    "esp_tanh": [P, P, c_int, c_longlong, P],
+    "esp_token_shift_mix": [P, c_int, P, c_longlong, P, P, P, P, P, c_int, c_int, c_int, P],
+    "esp_token_shift_keep": [P, c_int, P, c_longlong, P, P, c_int, c_int, P],
+    "esp_gated_scan": [c_int, P, c_longlong, P, c_longlong, P, c_longlong, P, c_longlong, P, P, P, P, c_longlong, P, P, P,
+                       c_int, c_int, c_int, c_int, P],
+    "esp_head_rmsnorm_gate": [P, P, c_int, P, c_longlong, P, c_int, c_int, c_int, c_int, c_float, P],
+    "esp_latent_kv_store": [P, P, P, c_float, c_int, P, P, P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_float, P,
+                            P],
+    "esp_latent_q_rotate": [P, P, c_float, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
+    "esp_per_head_linear": [P, c_int, c_longlong, c_int, P, c_int, P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, P],
+    "esp_attn_latent": [P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P, P],
     "esp_swiglu": [P, P, c_int, c_longlong, c_int, P],
     "esp_finite_check": [P, c_int, c_longlong, P, c_int, P],
     "esp_normal_fill": [P, c_int, c_longlong, c_ulonglong, c_float, c_float, P],
@@ -197,19 +210,47 @@ def feed_tokens(ids, picks, src):
                                            _ptr(src, torch.int32, "src"), ids.shape[0], _stream()), "feed_tokens")
 
 
-def add_rmsnorm(x, y, gamma, h, eps, rows=None, write_x=True, h32=None):
+def add_rmsnorm(x, y, gamma, h, eps, rows=None, write_x=True, h32=None, yscale=None):
     """h = rmsnorm(x + y) * gamma with x (+= y when write_x) float32, gamma
     float32, h float32 or bfloat16.  ``rows`` (int32) selects source rows;
-    ``h32`` (float32, same shape as h) receives the unrounded rows."""
+    ``h32`` (float32, same shape as h) receives the unrounded rows; ``yscale``
+    (float32 [width]) multiplies y channel by channel before it is added."""
     n_rows = h.shape[0]
     width = h.shape[1]
     if x.shape[1] != width or gamma.shape[0] != width:
         raise Backend("add_rmsnorm: widths disagree")
     _check(_fn("core", "esp_add_rmsnorm")(
-        _ptr(x, torch.float32, "x"), _ptr(y, torch.float32, "y"), _ptr(gamma, torch.float32, "gamma"),
+        _ptr(x, torch.float32, "x"), _ptr(y, torch.float32, "y"), _ptr(yscale, torch.float32, "yscale"),
+        _ptr(gamma, torch.float32, "gamma"),
         _ptr(rows, torch.int32, "rows"), _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(h32, torch.float32, "h32"), n_rows,
         width, float(eps),
         1 if write_x else 0, _stream()), "add_rmsnorm")
+
+
+def depth_mix(x, y, yscale, history, weights, index: int):
+    """Ends layer ``index`` of a model that averages over depth: history[index + 1] = x + y * yscale (y may be
+    None), then x = sum_j weights[j] * history[j] over j = 0 .. index + 1.  All float32; history
+    [depth, rows, width]."""
+    n, width = x.shape
+    if history.shape[0] < index + 2 or tuple(history.shape[1:]) != (n, width) or weights.shape[0] < index + 2:
+        raise Backend("depth_mix: the history or the weights are too short for this layer")
+    _check(_fn("core", "esp_depth_mix")(
+        _ptr(x, torch.float32, "x"), _ptr(y, torch.float32, "y"), _ptr(yscale, torch.float32, "yscale"),
+        _ptr(history, torch.float32, "history"), _ptr(weights, torch.float32, "weights"), int(index), n, width, _stream()),
+        "depth_mix")
+
+
+def xielu(z, pq, act):
+    """act = xIELU(z) with the two raw numbers ``pq`` (float32 [2] on the device); z float32, act float32 or bfloat16."""
+    if act.shape != z.shape:
+        raise Backend("xielu: shapes disagree")
+    _check(_fn("core", "esp_xielu")(_ptr(z, torch.float32, "z"), _ptr(pq, torch.float32, "pq"), _ptr(act, FLOATS, "act"),
+                                    _is_bf16(act), z.numel(), _stream()), "xielu")
+
+
+def tanh(z, out):
+    _check(_fn("core", "esp_tanh")(_ptr(z, torch.float32, "z"), _ptr(out, FLOATS, "out"), _is_bf16(out), z.numel(),
+                                   _stream()), "tanh")
 
 
 def swiglu(gu, act):
@@ -614,3 +655,117 @@ def wait_probe(polls: int, status):
     """Runs the library's bounded wait on a barrier that nothing completes: after ``polls`` tries the
     kernel sets the wait-expired bit of ``status`` and returns."""
     _check(_fn("tc05", "esp_wait_probe")(int(polls), _ptr(status, torch.int32, "status"), _stream()), "wait_probe")
+
+
+# ---------------------------------------------------------------------------
+# recurrent layers and latent attention (library "mixers")
+# ---------------------------------------------------------------------------
+def _rows_ld(t, what):
+    """(pointer, row stride) of a float32 matrix whose rows may be parts of wider rows."""
+    if t is None:
+        return None, 0
+    if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+        raise Backend(f"{what} must be a float32 matrix on the GPU with unit column stride")
+    return t.data_ptr(), t.stride(0)
+
+
+def token_shift_mix(h, prev_state, tok_seq, seq_start, seq_slot, mu, out):
+    """out[m, n] = h[n] + (prev(n) - h[n]) * mu[m]: prev(n) is the row before n in its sequence, or, for the
+    first row of the sequence in this step, the sequence's row of ``prev_state`` (float32 [slots, width], rows
+    may be parts of wider rows)."""
+    n, width = h.shape
+    if tuple(out.shape) != (mu.shape[0], n, width) or prev_state.shape[1] != width or prev_state.stride(1) != 1:
+        raise Backend("token_shift_mix: shapes disagree")
+    _check(_fn("mixers", "esp_token_shift_mix")(
+        _ptr(h, FLOATS, "h"), _is_bf16(h), prev_state.data_ptr(), prev_state.stride(0), _ptr(tok_seq, torch.int32),
+        _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(mu, torch.float32, "mu"), _ptr(out, h.dtype, "out"),
+        mu.shape[0], n, width, _stream()), "token_shift_mix")
+
+
+def token_shift_keep(h, prev_state, seq_start, seq_slot, n_seqs: int):
+    """prev_state[slot of sequence b] = the last row that b brings in this step."""
+    width = h.shape[1]
+    if prev_state.shape[1] != width or prev_state.stride(1) != 1 or prev_state.dtype != torch.float32:
+        raise Backend("token_shift_keep: the state rows must be float32 of the rows' width")
+    _check(_fn("mixers", "esp_token_shift_keep")(
+        _ptr(h, FLOATS, "h"), _is_bf16(h), prev_state.data_ptr(), prev_state.stride(0), _ptr(seq_start, torch.int32),
+        _ptr(seq_slot, torch.int32), int(n_seqs), width, _stream()), "token_shift_keep")
+
+
+SCAN_DECAY_BONUS = 0          # d = exp(-exp(g + bias)), the current token weighted by ``bonus``, output before the update
+SCAN_LOWER_SIGMOID = 1        # d = lower + (1 - lower) sigmoid(g + bias), k = 1 - d, q = silu(q), output after the update
+SCAN_MAX_KEY_DIM = 128
+
+
+def gated_scan(mode, q, k, g, v, gate_bias, lower, bonus, state, seq_start, seq_slot, out, n_seqs, heads, key_dim, value_dim):
+    """The gated outer-product recurrence S_t = diag(d_t) S_(t-1) + k_t v_t^T per head with its output, over the
+    runs of rows that the sequences bring (seq_start), from and to ``state`` (float32 [slots, >= heads * value_dim *
+    key_dim], a head's block laid out [value_dim, key_dim]).  q, k, g: float32 [rows, heads * key_dim]; v: float32
+    [rows, heads * value_dim]; out: float32 [rows, heads * value_dim].  All 32-bit."""
+    if key_dim > SCAN_MAX_KEY_DIM:
+        raise Backend(f"gated_scan: {key_dim} key channels per head are beyond the {SCAN_MAX_KEY_DIM} this kernel takes")
+    if state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] < heads * key_dim * value_dim:
+        raise Backend("gated_scan: the state rows are too short or not float32")
+    (pq, ldq), (pk, ldk), (pg, ldg), (pv, ldv) = (_rows_ld(t, n) for t, n in ((q, "q"), (k, "k"), (g, "g"), (v, "v")))
+    _check(_fn("mixers", "esp_gated_scan")(
+        int(mode), pq, ldq, pk, ldk, pg, ldg, pv, ldv, _ptr(gate_bias, torch.float32, "gate_bias"),
+        _ptr(lower, torch.float32, "lower"), _ptr(bonus, torch.float32, "bonus"), state.data_ptr(), state.stride(0),
+        _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(out, torch.float32, "out"), int(n_seqs), heads,
+        key_dim, value_dim, _stream()), "gated_scan")
+
+
+def head_rmsnorm_gate(o, weight, weight_head_stride, gate, y, heads, value_dim, eps):
+    """y[n, h] = o[n, h] / rms(o[n, h]) * weight[h * weight_head_stride + :] (* silu(gate[n, h])); o float32
+    [rows, heads * value_dim], gate float32 or None, y float32 or bfloat16."""
+    pg, ldg = _rows_ld(gate, "gate")
+    _check(_fn("mixers", "esp_head_rmsnorm_gate")(
+        _ptr(o, torch.float32, "o"), _ptr(weight, torch.float32, "weight"), int(weight_head_stride), pg, ldg,
+        _ptr(y, FLOATS, "y"), _is_bf16(y), o.shape[0], heads, value_dim, float(eps), _stream()), "head_rmsnorm_gate")
+
+
+def latent_kv_store(d, norm_w, inv_freq, magnitude, rot_dims, tok_seq, tok_pos, block_table, pool, page, rank, rot, eps, status):
+    """Rows of the latent cache from the down-projection's output d (float32 [rows, rank + rot]): the first
+    ``rank`` channels RMS-normed times norm_w, the last ``rot`` rotated (the first rot_dims of them, in pairs
+    (i, i + rot_dims/2), angle position * inv_freq[i], cos and sin times ``magnitude``).  pool: [pages, 1, page,
+    rank + rot]."""
+    if d.shape[1] != rank + rot or pool.shape[-1] != rank + rot:
+        raise Backend("latent_kv_store: widths disagree")
+    _check(_fn("mixers", "esp_latent_kv_store")(
+        _ptr(d, torch.float32, "d"), _ptr(norm_w, torch.float32, "norm_w"), _ptr(inv_freq, torch.float32, "inv_freq"),
+        float(magnitude), int(rot_dims), _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32),
+        _ptr(block_table, torch.int32), block_table.shape[1], pool.shape[0], page, _ptr(pool, FLOATS, "pool"), _is_bf16(pool),
+        d.shape[0], rank, rot, float(eps), _ptr(status, torch.int32), _stream()), "latent_kv_store")
+
+
+def latent_q_rotate(q, inv_freq, magnitude, rot_dims, tok_pos, qx, heads, nope, rot, rank):
+    """qx[n, h, rank:] = rotation of q[n, h, nope:] (q float32 [rows, heads * (nope + rot)]; qx [rows, heads *
+    (rank + rot)])."""
+    _check(_fn("mixers", "esp_latent_q_rotate")(
+        _ptr(q, torch.float32, "q"), _ptr(inv_freq, torch.float32, "inv_freq"), float(magnitude), int(rot_dims),
+        _ptr(tok_pos, torch.int32), _ptr(qx, FLOATS, "qx"), _is_bf16(qx), q.shape[0], heads, nope, rot, rank, _stream()),
+        "latent_q_rotate")
+
+
+def per_head_linear(a, lda, a_head, w, out, ldo, o_head, n_rows, heads, kin, nout):
+    """out[n, h, :nout] = w[h] @ a[n, h, :kin] with w [heads, nout, kin]; element (n, h, i) of a lies at
+    n * lda + h * a_head + i (out likewise), so both may be parts of wider rows."""
+    if tuple(w.shape) != (heads, nout, kin) or kin * 8 * 4 > 48 * 1024:
+        raise Backend(f"per_head_linear: weights {tuple(w.shape)} do not fit heads {heads}, {nout} x {kin}")
+    code = {torch.float32: 0, torch.bfloat16: 1}
+    _check(_fn("mixers", "esp_per_head_linear")(
+        _ptr(a, FLOATS, "a"), code[a.dtype], int(lda), int(a_head), _ptr(w, FLOATS, "w"), code[w.dtype],
+        _ptr(out, FLOATS, "out"), code[out.dtype], int(ldo), int(o_head), int(n_rows), heads, kin, nout, _stream()),
+        "per_head_linear")
+
+
+def attn_latent(qx, pool, out, tok_seq, tok_pos, block_table, page, heads, key_dim, value_dim, window, scale, status):
+    """Attention of every head of every token over its sequence's cached rows (one row per position, shared by
+    the heads): scores from the whole row (key_dim), values the row's first value_dim channels.  32-bit
+    arithmetic; qx, pool and out share a dtype."""
+    if pool.shape[-1] != key_dim or value_dim > 512:
+        raise Backend(f"attn_latent: rows of {pool.shape[-1]} / values of {value_dim} channels not taken")
+    _check(_fn("mixers", "esp_attn_latent")(
+        _ptr(qx, FLOATS, "qx"), _ptr(pool, qx.dtype, "pool"), _ptr(out, qx.dtype, "out"), _is_bf16(qx),
+        _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(block_table, torch.int32), block_table.shape[1],
+        pool.shape[0], page, qx.shape[0], heads, key_dim, value_dim, int(window or 0), float(scale),
+        _ptr(status, torch.int32), _stream()), "attn_latent")

@@ -1,0 +1,286 @@
+// Layers with a recurrent state of fixed size per sequence.
+//
+//  * token shift: every row is mixed with the row before it in its sequence (the last row of the step before comes
+//    from the sequence's state), once per consumer, each with a mixing vector of its own;
+//  * the gated outer-product recurrence that linear-attention layers share,
+//        S_t = diag(d_t) S_(t-1) + k_t v_t^T          S: [K, V] per head, 32-bit, one per sequence
+//        o_t = (S_(t-1) or S_t, + diag(b) k_t v_t^T)^T q_t
+//    with the gates made from the projections' raw outputs as the rows are staged (so that decays, their
+//    exponentials and the sigmoid never leave 32-bit);
+//  * the per-head RMS norm of the recurrence's output with an optional SiLU gate.
+//
+// The recurrence is sequential in t by definition and everything that enters it is 32-bit, so it runs on the CUDA
+// cores: a block owns (sequence, head, a tile of value columns), a thread a value column and a slice of the key
+// channels, which it keeps in registers for the whole run of tokens.  Tokens are staged CHUNK at a time through two
+// shared-memory buffers filled by cp.async, so the loop over tokens never waits for global memory; inside a chunk no
+// block-wide barrier is needed (the key slices of a column sit in neighbouring lanes and are added by shuffles).
+// The order of every addition depends on the token and the channel alone: cutting a sequence into steps, or
+// batching it with others, changes no bit.
+#include "common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------- token shift
+// out[m, n, :] = h[n] + (prev(n) - h[n]) * mu[m];  prev(n) = h[n - 1] within the step's run of the sequence, or the
+// sequence's state row for the run's first token (zeros for a sequence's first token: a fresh slot is zeroed).
+template <typename T>
+__global__ void token_shift_mix_kernel(const T* __restrict__ h, const float* __restrict__ prev_state, long long state_stride,
+                                       const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                                       const int* __restrict__ seq_slot, const float* __restrict__ mu, T* __restrict__ out,
+                                       int n_mix, int n_rows, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int seq = tok_seq[n];
+    const bool first = n == seq_start[seq];
+    const float* ps = prev_state + (size_t)seq_slot[seq] * state_stride;
+    const T* cur = h + (size_t)n * width;
+    const T* before = h + (size_t)(n - 1) * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        const float c = to_f32(cur[d]);
+        const float p = first ? ps[d] : to_f32(before[d]);
+        const float diff = p - c;
+        for (int m = 0; m < n_mix; m++)
+            out[((size_t)m * n_rows + n) * width + d] = from_f32<T>(fmaf(diff, mu[(size_t)m * width + d], c));
+    }
+}
+
+// state row of every sequence <- its last row of the step
+template <typename T>
+__global__ void token_shift_keep_kernel(const T* __restrict__ h, float* __restrict__ prev_state, long long state_stride,
+                                        const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int last = seq_start[b + 1] - 1;
+    if (last < seq_start[b]) return;
+    float* ps = prev_state + (size_t)seq_slot[b] * state_stride;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) ps[d] = to_f32(h[(size_t)last * width + d]);
+}
+
+// ---------------------------------------------------------------------------------------------- the recurrence
+constexpr int SCAN_THREADS = 128;
+constexpr int KT = 16;          // key channels a thread keeps
+constexpr int CHUNK = 16;       // tokens staged at a time
+constexpr int MAX_K = 8 * KT;   // key channels of a head that the kernel takes
+
+enum : int {
+    GATE_EXP_EXP = 0,      // d = exp(-exp(g + bias));  k, q as given;  o reads S_(t-1) + diag(bonus) k v^T
+    GATE_LOWER_SIGMOID = 1 // d = lower + (1 - lower) * sigmoid(g + bias);  k = 1 - d;  q = silu(q);  o reads S_t
+};
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+// q, k, g: [rows, ld*] float (k may be null in GATE_LOWER_SIGMOID); v: [rows, ldv]; head h reads columns
+// [h*K, (h+1)*K) (v: [h*V, (h+1)*V)).  state: [slots, state_stride] floats, the head's block at h*V*K laid out
+// [V][K] (a thread's key slice is contiguous).  out: [rows, H*V] float.
+template <int MODE>
+__global__ void __launch_bounds__(SCAN_THREADS)
+gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
+                  const float* __restrict__ g, long long ldg, const float* __restrict__ v, long long ldv,
+                  const float* __restrict__ gate_bias, const float* __restrict__ lower, const float* __restrict__ bonus,
+                  float* __restrict__ state, long long state_stride, const int* __restrict__ seq_start,
+                  const int* __restrict__ seq_slot, float* __restrict__ out, int H, int K, int V, int ks, int vt) {
+    pdl_trigger();
+    extern __shared__ float smem[];
+    const int kp = ks * KT;                        // key channels, padded to the threads' slices
+    // per buffer: q[CHUNK][kp], k[CHUNK][kp], d[CHUNK][kp], v[CHUNK][vt]
+    const int buf_floats = CHUNK * (3 * kp + vt);
+    const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * vt;
+    const int tid = threadIdx.x;
+    const int part = tid % ks, col = tid / ks;     // neighbouring lanes hold the slices of one column
+    const int vcol = v0 + col;
+    const bool live = col < vt && vcol < V;
+    const int row0 = seq_start[b], row1 = seq_start[b + 1];
+    if (row1 <= row0) return;
+    float* srow = state + (size_t)seq_slot[b] * state_stride + ((size_t)h * V + (live ? vcol : 0)) * K + part * KT;
+
+    // constants of the head: bias / lower bound / bonus per key channel
+    __shared__ float c_bias[MAX_K], c_lower[MAX_K], c_bonus[MAX_K];
+    for (int i = tid; i < kp; i += SCAN_THREADS) {
+        const bool in = i < K;
+        c_bias[i] = in && gate_bias ? gate_bias[h * K + i] : 0.f;
+        c_lower[i] = in && lower ? lower[h * K + i] : 0.f;
+        c_bonus[i] = in && bonus ? bonus[h * K + i] : 1.f;
+    }
+    // zero the padding of both buffers once (cp.async never writes it)
+    for (int i = tid; i < 2 * buf_floats; i += SCAN_THREADS) smem[i] = 0.f;
+    __syncthreads();
+
+    pdl_wait();
+    float S[KT];
+#pragma unroll
+    for (int i = 0; i < KT; i++) S[i] = (live && part * KT + i < K) ? srow[i] : 0.f;
+
+    auto stage = [&](int buffer, int r0) {
+        float* base = smem + buffer * buf_floats;
+        const int count = min(CHUNK, row1 - r0);
+        for (int i = tid; i < count * K; i += SCAN_THREADS) {
+            const int t = i / K, c = i - t * K;
+            const size_t r = (size_t)(r0 + t);
+            cp_async4(base + t * kp + c, q + r * ldq + h * K + c);
+            if (MODE == GATE_EXP_EXP) cp_async4(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
+            cp_async4(base + (2 * CHUNK + t) * kp + c, g + r * ldg + h * K + c);
+        }
+        for (int i = tid; i < count * vt; i += SCAN_THREADS) {
+            const int t = i / vt, c = i - t * vt;
+            if (v0 + c < V) cp_async4(base + 3 * CHUNK * kp + t * vt + c, v + (size_t)(r0 + t) * ldv + h * V + v0 + c);
+        }
+        cp_async_commit();
+    };
+
+    stage(0, row0);
+    int buffer = 0;
+    for (int r0 = row0; r0 < row1; r0 += CHUNK, buffer ^= 1) {
+        const int count = min(CHUNK, row1 - r0);
+        cp_async_wait_all();
+        __syncthreads();                            // the chunk has landed; everyone is done with the other buffer
+        if (r0 + CHUNK < row1) stage(buffer ^ 1, r0 + CHUNK);
+        float* base = smem + buffer * buf_floats;
+        float* sq = base, *sk = base + CHUNK * kp, *sd = base + 2 * CHUNK * kp, *sv = base + 3 * CHUNK * kp;
+        // gates, in place
+        for (int i = tid; i < count * K; i += SCAN_THREADS) {
+            const int t = i / K, c = i - t * K;
+            const float raw = sd[t * kp + c] + c_bias[c];
+            if (MODE == GATE_EXP_EXP) {
+                sd[t * kp + c] = expf(-expf(raw));
+            } else {
+                const float lo = c_lower[c];
+                const float d = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-raw)));
+                sd[t * kp + c] = d;
+                sk[t * kp + c] = 1.0f - d;
+                const float z = sq[t * kp + c];
+                sq[t * kp + c] = z / (1.0f + expf(-z));
+            }
+        }
+        __syncthreads();
+        for (int t = 0; t < count; t++) {
+            const float* tq = sq + t * kp + part * KT, *tk = sk + t * kp + part * KT, *td = sd + t * kp + part * KT;
+            const float vv = live ? sv[t * vt + col] : 0.f;
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < KT; i++) {
+                const float a = tk[i] * vv;
+                if (MODE == GATE_EXP_EXP) {
+                    o = fmaf(tq[i], fmaf(c_bonus[part * KT + i], a, S[i]), o);
+                    S[i] = fmaf(td[i], S[i], a);
+                } else {
+                    S[i] = fmaf(td[i], S[i], a);
+                    o = fmaf(tq[i], S[i], o);
+                }
+            }
+            for (int off = 1; off < ks; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            if (live && part == 0) out[(size_t)(r0 + t) * H * V + h * V + vcol] = o;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < KT; i++)
+            if (part * KT + i < K) srow[i] = S[i];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- norm of the heads
+// y[n, h, :] = o[n, h, :] / sqrt(mean(o[n, h, :]^2) + eps) * w[h * w_head_stride + :] (* silu(gate[n, h, :]))
+// One warp per (row, head).
+template <typename T>
+__global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const float* __restrict__ w, int w_head_stride,
+                                         const float* __restrict__ gate, long long ldgate, T* __restrict__ y, int n_rows,
+                                         int H, int V, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_rows * H) return;
+    const int n = warp / H, h = warp - n * H;
+    const float* src = o + ((size_t)n * H + h) * V;
+    float ss = 0.f;
+    for (int i = lane; i < V; i += 32) ss = fmaf(src[i], src[i], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+    for (int i = lane; i < V; i += 32) {
+        float r = src[i] * inv * w[h * w_head_stride + i];
+        if (gate) {
+            const float z = gate[(size_t)n * ldgate + h * V + i];
+            r *= z / (1.0f + expf(-z));
+        }
+        y[((size_t)n * H + h) * V + i] = from_f32<T>(r);
+    }
+}
+}  // namespace
+
+ESP_API int esp_token_shift_mix(const void* h, int is_bf16, const float* prev_state, long long state_stride,
+                                const int* tok_seq, const int* seq_start, const int* seq_slot, const float* mu, void* out,
+                                int n_mix, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, token_shift_mix_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, (const bf16*)h,
+                       prev_state, state_stride, tok_seq, seq_start, seq_slot, mu, (bf16*)out, n_mix, n_rows, width);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, token_shift_mix_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, (const float*)h,
+                       prev_state, state_stride, tok_seq, seq_start, seq_slot, mu, (float*)out, n_mix, n_rows, width);
+    return esp_launch_status();
+}
+
+ESP_API int esp_token_shift_keep(const void* h, int is_bf16, float* prev_state, long long state_stride, const int* seq_start,
+                                 const int* seq_slot, int n_seqs, int width, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, token_shift_keep_kernel<bf16>, dim3(n_seqs), dim3(128), 0, stream, (const bf16*)h,
+                       prev_state, state_stride, seq_start, seq_slot, width);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, token_shift_keep_kernel<float>, dim3(n_seqs), dim3(128), 0, stream, (const float*)h,
+                       prev_state, state_stride, seq_start, seq_slot, width);
+    return esp_launch_status();
+}
+
+// mode: 0 = decay exp(-exp(.)) with a bonus for the current token, 1 = lower-bounded sigmoid gate that also writes.
+ESP_API int esp_gated_scan(int mode, const float* q, long long ldq, const float* k, long long ldk, const float* g,
+                           long long ldg, const float* v, long long ldv, const float* gate_bias, const float* lower,
+                           const float* bonus, float* state, long long state_stride, const int* seq_start,
+                           const int* seq_slot, float* out, int n_seqs, int H, int K, int V, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (K <= 0 || V <= 0 || K > MAX_K || H > 65535) return (int)cudaErrorInvalidValue;
+    int ks = 1;
+    while (ks * KT < K) ks <<= 1;                  // 1, 2, 4 or 8 slices of KT channels
+    if (ks > 8) return (int)cudaErrorInvalidValue;
+    const int vt = SCAN_THREADS / ks;              // value columns of a block
+    const int vtiles = (V + vt - 1) / vt;
+    const size_t smem = 2 * (size_t)CHUNK * (3 * ks * KT + vt) * sizeof(float);
+    dim3 grid(n_seqs, H, vtiles);
+    if (mode == GATE_EXP_EXP) {
+        if (!k) return (int)cudaErrorInvalidValue;
+        static bool set0 = false;
+        if (!set0) { cudaFuncSetAttribute(gated_scan_kernel<GATE_EXP_EXP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set0 = true; }
+        esp_launch_pdl(ESP_PDL_SMALL, gated_scan_kernel<GATE_EXP_EXP>, grid, dim3(SCAN_THREADS), smem, stream, q, ldq, k, ldk,
+                       g, ldg, v, ldv, gate_bias, lower, bonus, state, state_stride, seq_start, seq_slot, out, H, K, V, ks, vt);
+    } else if (mode == GATE_LOWER_SIGMOID) {
+        static bool set1 = false;
+        if (!set1) { cudaFuncSetAttribute(gated_scan_kernel<GATE_LOWER_SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set1 = true; }
+        esp_launch_pdl(ESP_PDL_SMALL, gated_scan_kernel<GATE_LOWER_SIGMOID>, grid, dim3(SCAN_THREADS), smem, stream, q, ldq, k,
+                       ldk, g, ldg, v, ldv, gate_bias, lower, bonus, state, state_stride, seq_start, seq_slot, out, H, K, V,
+                       ks, vt);
+    } else {
+        return (int)cudaErrorInvalidValue;
+    }
+    return esp_launch_status();
+}
+
+ESP_API int esp_head_rmsnorm_gate(const float* o, const float* w, int w_head_stride, const float* gate, long long ldgate,
+                                  void* y, int y_is_bf16, int n_rows, int H, int V, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const long long warps = (long long)n_rows * H;
+    const int blocks = (int)((warps + 7) / 8);
+    if (y_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, head_rmsnorm_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, o, w, w_head_stride,
+                       gate, ldgate, (bf16*)y, n_rows, H, V, eps);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, head_rmsnorm_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, o, w, w_head_stride,
+                       gate, ldgate, (float*)y, n_rows, H, V, eps);
+    return esp_launch_status();
+}

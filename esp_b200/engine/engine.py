@@ -80,7 +80,7 @@ class Engine:
             self.model = DecoderModel(self.plan, self.rt)
             specs = [s for part in self.model.all_parts() for s in part.param_specs()]
             source = source_factory(specs)
-            self.memory_plan = self._check_memory(specs, source, max_tokens, shrink_to_fit)
+            self.memory_plan = self._check_memory(specs, source, max_tokens, shrink_to_fit, max_slots)
             max_tokens = self.memory_plan["cache_tokens"]
             self.max_tokens = max_tokens
             load_into(self.model, source, self.rt)
@@ -118,7 +118,7 @@ class Engine:
         self._graph_seen: dict = {}
         self.graph_replays = 0
 
-    def _check_memory(self, specs, source, max_tokens: int, shrink: bool) -> dict:
+    def _check_memory(self, specs, source, max_tokens: int, shrink: bool, max_slots=None) -> dict:
         """Bytes of weights and cache that this engine is about to allocate against
         the device's free memory; refuses with the numbers instead of dying inside
         an allocation.  ``ESP_B200_MEMORY_HEADROOM`` (bytes, default 2 GiB) is kept
@@ -133,10 +133,15 @@ class Engine:
             kept = self.rt.matrix_dtype([source.dtype(sp.name)]) if sp.role == "matrix" else torch.float32
             weights += count * el.get(kept, 4)
         tokens = (max_tokens + 63) // 64 * 64
-        per_token = 0
-        for layout, _state, cache_of in self.model.cache_requests():
+        per_token, per_slot = 0, 0
+        for layout, state, cache_of in self.model.cache_requests():
             if layout is not None and cache_of is None:
-                per_token += 2 * layout.num_kv_heads * layout.head_dim * el[self.dtype]
+                per_token += (2 if layout.values else 1) * layout.num_kv_heads * layout.head_dim * el[self.dtype]
+            if state is not None:
+                per_slot += int(np.prod(state.shape)) * el.get(state.dtype, 4)
+        # the mixers' states of fixed size: one row per slot
+        slots = max_slots if max_slots is not None else max(1, min((max_tokens + 63) // 64, 4096))
+        weights += per_slot * slots
         cache = per_token * tokens
         free, total = torch.cuda.mem_get_info(self.rt.device)
         headroom = int(os.environ.get("ESP_B200_MEMORY_HEADROOM", 2 << 30))
@@ -157,6 +162,9 @@ class Engine:
     def from_folder(cls, folder, **kw) -> "Engine":
         folder = Path(folder)
         config = config_from_json(folder)
+        if hasattr(config, "bind_shapes"):        # sizes that the configuration leaves to the stored tensors
+            probe = FolderSource(folder)
+            config.bind_shapes({n: probe.shape(n) for n in probe.names()})
         return cls(config, lambda specs: FolderSource(folder), **kw)
 
     @classmethod
@@ -356,7 +364,7 @@ class Engine:
         c["tokens"] += sum(news)
         el = torch.empty((), dtype=self.dtype).element_size()
         for layout, members in zip(self.cache.layouts, self.cache.members):
-            per_key = 2 * len(members) * layout.num_kv_heads * layout.head_dim * el
+            per_key = (2 if layout.values else 1) * len(members) * layout.num_kv_heads * layout.head_dim * el
             seen = 0
             for p, t in zip(pasts, news):
                 # the keys the sequence's last new token sees: every kernel streams a sequence's visible keys once

@@ -50,6 +50,7 @@ class ParamSpec:
     shape: tuple
     role: str                 # "matrix" | "bias" | "norm_scale"
     optional: bool = False
+    init: Optional[tuple] = None   # (mean, std) of random weights for this tensor, where the role's rule does not fit
 
 
 @dataclass(frozen=True)

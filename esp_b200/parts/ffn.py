@@ -86,6 +86,44 @@ class DenseSwiGlu(Part):
         return y
 
 
+class DenseXielu(Part):
+    """y = W_down xIELU(W_up h): for z > 0 softplus(p) z^2 + z/2, else (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2,
+    p and q being the two numbers of the activation's tensor."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.w_up = self.w_down = self.pq = None
+
+    def param_specs(self):
+        s, p = self.spec, self.spec.prefix
+        return [ParamSpec(p + s.up, (s.intermediate, s.hidden), "matrix"),
+                ParamSpec(p + s.down, (s.hidden, s.intermediate), "matrix"),
+                ParamSpec(p + s.act, (2,), "activation", init=(0.5, 0.3))]
+
+    def allocate(self, stored, rt):
+        s, p = self.spec, self.spec.prefix
+        self.w_up = torch.empty((s.intermediate, s.hidden), dtype=rt.matrix_dtype([stored[p + s.up]]), device=rt.device)
+        self.w_down = torch.empty((s.hidden, s.intermediate), dtype=rt.matrix_dtype([stored[p + s.down]]), device=rt.device)
+        self.pq = torch.empty(2, dtype=torch.float32, device=rt.device)
+        return {p + s.up: self.w_up, p + s.down: self.w_down, p + s.act: self.pq}
+
+    def forward(self, h, ctx, h32=None):
+        rt, s = self.rt, self.spec
+        n = h.shape[0]
+        y = rt.ws.get("ffn_out", (n, s.hidden), torch.float32)
+        step = rt.ffn_chunk_tokens
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            z = rt.ws.get("xielu_z", (b - a, s.intermediate), torch.float32)
+            linear(rt, h[a:b], self.w_up, z)
+            act = rt.ws.get("xielu_act", (b - a, s.intermediate), rt.dtype)
+            ops.xielu(z, self.pq, act)
+            linear(rt, act, self.w_down, y[a:b])
+        return y
+
+
 class MoeSwiGluShared(Part):
     """Router (32-bit softmax over all experts, top-k, ties to the lower id,
     optional renormalisation), routed SwiGLU experts whose outputs are scaled
@@ -246,4 +284,5 @@ class MoeSwiGluShared(Part):
 
 
 register("ffn", "swiglu", DenseSwiGlu)
+register("ffn", "xielu", DenseXielu)
 register("ffn", "moe_swiglu_shared", MoeSwiGluShared)

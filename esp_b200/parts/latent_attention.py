@@ -1,0 +1,117 @@
+"""Attention through a cached low-rank latent, with a sliding window and a rotated key part shared by the heads."""
+from __future__ import annotations
+
+import torch
+
+from ..cache import KvLayout
+from ..csrc import ops
+from .base import ParamSpec, Part, build, register
+from .linear import linear
+
+
+class LatentAttention(Part):
+    """c_q = norm(W_dq h), q = W_uq c_q laid out per head as [nope | rot]; W_dkv h gives the latent c (its first
+    kv_rank rows, normed) and one rotated key part for all heads; per head the unrotated key is W_uk c and the value
+    W_uv c; score = (q_nope . k_nope + q_rot . k_rot) * scale over the window; softmax; W_o on the heads.
+
+    Only c and the rotated key part are cached, one row [c | k_rot] per position.  The keys' up-projection is
+    folded into the query (q_lat = W_uk^T q_nope per head) and the values' up-projection is applied to the
+    weighted sum of latents, so every head attends to the cached rows themselves.  A layer without a
+    down-projection of its own (``own_kv`` False) reads the rows another layer cached, with its own window."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        key = ("position", spec.position)
+        if key not in rt.shared_parts:
+            rt.shared_parts[key] = build("position", spec.position, rt)
+        self.position = rt.shared_parts[key]
+        self.row = spec.kv_rank + spec.rot_dim
+        self.q_head = spec.nope_dim + spec.rot_dim
+        self.w_dq = self.dq_norm = self.w_uq = self.w_dkv = self.dkv_norm = self.w_uk = self.w_uv = self.w_o = None
+        self.w_uk_t = None
+
+    def children(self):
+        return [self.position]
+
+    def _n(self, which):
+        return self.spec.prefix + getattr(self.spec.names, which)
+
+    def param_specs(self):
+        s = self.spec
+        specs = [ParamSpec(self._n("q_down"), (s.q_rank, s.hidden), "matrix"),
+                 ParamSpec(self._n("q_norm"), (s.q_rank,), "norm_scale"),
+                 ParamSpec(self._n("q_up"), (s.num_heads * self.q_head, s.q_rank), "matrix"),
+                 ParamSpec(self._n("k_up"), (s.num_heads * s.nope_dim, s.kv_rank), "matrix"),
+                 ParamSpec(self._n("v_up"), (s.num_heads * s.value_dim, s.kv_rank), "matrix"),
+                 ParamSpec(self._n("o"), (s.hidden, s.num_heads * s.value_dim), "matrix")]
+        if s.own_kv:
+            specs += [ParamSpec(self._n("kv_down"), (self.row, s.hidden), "matrix"),
+                      ParamSpec(self._n("kv_norm"), (s.kv_rank,), "norm_scale")]
+        return specs
+
+    def allocate(self, stored, rt):
+        s, dev = self.spec, rt.device
+        mat = lambda which, *shape: torch.empty(shape, dtype=rt.matrix_dtype([stored[self._n(which)]]), device=dev)
+        self.w_dq = mat("q_down", s.q_rank, s.hidden)
+        self.w_uq = mat("q_up", s.num_heads * self.q_head, s.q_rank)
+        self.w_uk = mat("k_up", s.num_heads * s.nope_dim, s.kv_rank)
+        self.w_uv = mat("v_up", s.num_heads * s.value_dim, s.kv_rank)
+        self.w_o = mat("o", s.hidden, s.num_heads * s.value_dim)
+        self.dq_norm = torch.empty(s.q_rank, dtype=torch.float32, device=dev)
+        views = {self._n("q_down"): self.w_dq, self._n("q_up"): self.w_uq, self._n("k_up"): self.w_uk,
+                 self._n("v_up"): self.w_uv, self._n("o"): self.w_o, self._n("q_norm"): self.dq_norm}
+        if s.own_kv:
+            self.w_dkv = mat("kv_down", self.row, s.hidden)
+            self.dkv_norm = torch.empty(s.kv_rank, dtype=torch.float32, device=dev)
+            views.update({self._n("kv_down"): self.w_dkv, self._n("kv_norm"): self.dkv_norm})
+        return views
+
+    def finalize(self):
+        s = self.spec
+        if self.w_uk is not None and self.w_uk_t is None:
+            # per head [kv_rank, nope]: the product that folds the keys' up-projection into the query reads it row by row
+            self.w_uk_t = self.w_uk.view(s.num_heads, s.nope_dim, s.kv_rank).transpose(1, 2).contiguous()
+            self.w_uk = None
+
+    # -- what it keeps per sequence ------------------------------------------------
+    def kv_layout(self):
+        # one row per position for all heads, no separate values: they are the row's first kv_rank channels
+        return KvLayout(1, self.row, self.spec.keep_window, values=False)
+
+    def state_spec(self):
+        return None
+
+    def forward(self, h, ctx, layer):
+        s, rt, pos = self.spec, self.rt, self.position
+        n, H = h.shape[0], s.num_heads
+        table = ctx.block_tables[layer.group]
+        dq = rt.ws.get("la_dq", (n, s.q_rank), torch.float32)
+        linear(rt, h, self.w_dq, dq)
+        cq = rt.ws.get("la_cq", (n, s.q_rank), rt.dtype)
+        ops.add_rmsnorm(dq, None, self.dq_norm, cq, s.eps, write_x=False)
+        q = rt.ws.get("la_q", (n, H * self.q_head), torch.float32)
+        linear(rt, cq, self.w_uq, q)
+        if layer.writes:
+            d = rt.ws.get("la_dkv", (n, self.row), torch.float32)
+            linear(rt, h, self.w_dkv, d)
+            ops.latent_kv_store(d, self.dkv_norm, pos.inv_freq, pos.magnitude, pos.spec.rotary_dim, ctx.tok_seq, ctx.tok_pos,
+                                table, layer.k, layer.page, s.kv_rank, s.rot_dim, s.eps, rt.status)
+        qx = rt.ws.get("la_qx", (n, H * self.row), rt.dtype)
+        ops.latent_q_rotate(q, pos.inv_freq, pos.magnitude, pos.spec.rotary_dim, ctx.tok_pos, qx, H, s.nope_dim, s.rot_dim,
+                            s.kv_rank)
+        ops.per_head_linear(q, H * self.q_head, self.q_head, self.w_uk_t, qx, H * self.row, self.row, n, H, s.nope_dim,
+                            s.kv_rank)
+        o_lat = rt.ws.get("la_olat", (n, H * s.kv_rank), rt.dtype)
+        ops.attn_latent(qx, layer.k, o_lat, ctx.tok_seq, ctx.tok_pos, table, layer.page, H, self.row, s.kv_rank, s.window,
+                        s.scale, rt.status)
+        o = rt.ws.get("la_o", (n, H * s.value_dim), rt.dtype)
+        ops.per_head_linear(o_lat, H * s.kv_rank, s.kv_rank, self.w_uv.view(H, s.value_dim, s.kv_rank), o, H * s.value_dim,
+                            s.value_dim, n, H, s.kv_rank, s.value_dim)
+        y = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
+        linear(rt, o, self.w_o, y)
+        return y
+
+
+register("mixer", "latent_attention", LatentAttention)

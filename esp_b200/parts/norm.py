@@ -26,12 +26,16 @@ class RmsNorm(Part):
         self.weight = torch.empty(self.spec.width, dtype=torch.float32, device=rt.device)
         return {self.spec.weight: self.weight}
 
-    def forward(self, x, delta, h, rows=None, write_x=True, h32=None):
+    def forward(self, x, delta, h, rows=None, write_x=True, h32=None, delta_scale=None):
+        """``delta_scale`` (float32 [width]): delta is multiplied by it channel by channel as it is added."""
+        if hasattr(delta, "fused_add_rmsnorm") and delta_scale is not None:
+            delta = delta.materialize()
         if hasattr(delta, "fused_add_rmsnorm"):
             # the producer left its last step (an ordered sum) to be done here, in the same launch
             delta.fused_add_rmsnorm(x, self.weight, h, self.spec.eps, rows, write_x, h32)
             return h
-        ops.add_rmsnorm(x, delta, self.weight, h, self.spec.eps, rows=rows, write_x=write_x, h32=h32)
+        ops.add_rmsnorm(x, delta, self.weight, h, self.spec.eps, rows=rows, write_x=write_x, h32=h32,
+                        yscale=delta_scale if delta is not None else None)
         return h
 
 

@@ -63,5 +63,43 @@ class NoPosition(Part):
                          layer.page, nh, nkv, hd, layer.writes, status)
 
 
+class RopeScaled(Part):
+    """Split-half rotary encoding with interpolated slow frequencies (see ``ScaledRopeSpec``).  It keeps one
+    frequency per pair and the magnitude factor; kernels take the angle position * frequency in 32-bit where they
+    rotate, so no table bounds the positions.  With d = rotary_dim, base b and i = 0 .. d/2 - 1:
+        f_i = b^(-2i/d);  corr(t) = d ln(original / (2 pi t)) / (2 ln b)
+        lo = max(floor(corr(fast)), 0), hi = min(ceil(corr(slow)), d - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+        frequency_i = f_i / factor * ramp_i + f_i (1 - ramp_i);  magnitude = 0.1 ln(factor) + 1."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.inv_freq = None
+        self.magnitude = 1.0
+
+    def frequencies(self):
+        """(float32 [rotary_dim / 2], magnitude), on the host."""
+        sp = self.spec
+        i = np.arange(sp.rotary_dim // 2, dtype=np.float64)
+        f = np.power(float(sp.theta), -2.0 * i / sp.rotary_dim)
+        mag = 1.0
+        if sp.factor is not None:
+            def corr(turns):
+                return sp.rotary_dim * np.log(sp.original / (2.0 * np.pi * turns)) / (2.0 * np.log(sp.theta))
+            lo = max(int(np.floor(corr(sp.fast))), 0)
+            hi = min(int(np.ceil(corr(sp.slow))), sp.rotary_dim - 1)
+            ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / sp.factor * ramp + f * (1.0 - ramp)
+            mag = 0.1 * float(np.log(sp.factor)) + 1.0
+        return f.astype(np.float32), float(mag)
+
+    def finalize(self):
+        if self.inv_freq is None:
+            f, self.magnitude = self.frequencies()
+            self.inv_freq = torch.from_numpy(f).to(self.rt.device).contiguous()
+
+
 register("position", "rope_split_half", RopeSplitHalf)
+register("position", "rope_split_half_scaled", RopeScaled)
 register("position", "none", NoPosition)

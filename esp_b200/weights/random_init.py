@@ -103,9 +103,14 @@ class RandomSource:
     def shape(self, name):
         return tuple(self.specs[name].shape)
 
+    def _mean_std(self, s):
+        if getattr(s, "init", None) is not None:
+            return float(s.init[0]), float(s.init[1])
+        return self.init.mean_std(s.role)
+
     def host_tensor(self, name) -> torch.Tensor:
         s = self.specs[name]
-        mean, std = self.init.mean_std(s.role)
+        mean, std = self._mean_std(s)
         count = int(np.prod(s.shape)) if s.shape else 1
         vals = normal_values(tensor_key(self.seed, name), count, mean, std) if std > 0 else np.full(
             count, mean, dtype=np.float32)
@@ -113,7 +118,7 @@ class RandomSource:
 
     def read_into(self, name, view: torch.Tensor) -> None:
         s = self.specs[name]
-        mean, std = self.init.mean_std(s.role)
+        mean, std = self._mean_std(s)
         if view.is_cuda and view.is_contiguous() and view.dtype in (torch.float32, torch.bfloat16) and std > 0:
             from ..csrc import ops
             if view.dtype == self._dtype or self._dtype == torch.float32:
