@@ -173,3 +173,91 @@ def forward(cfg, weights, tokens, dtype=torch.float64, layers_out=None):
             layers_out.append(x.clone())
     h = rms(x, eps) * w["final.norm"]
     return h @ w["head"].T
+
+
+# ---------------------------------------------------------------------------------------------------------
+# tensors of a model, listed from the design (not from the library), and random values that keep every
+# mechanism alive: decays near one and near zero, bounds inside (0, 1), scales away from one
+def tensor_shapes(cfg, decay_rank=16):
+    D, shapes = cfg["width"], {}
+    shapes["embed"] = (cfg["vocab"], D)
+    shapes["head"] = (cfg["vocab"], D)
+    shapes["final.norm"] = (D,)
+    for i, layer in enumerate(cfg["layers"]):
+        p, mix = f"l{i}.", layer["mixer"]
+        shapes[p + "norm1"] = (D,)
+        shapes[p + "ls1"] = (D,)
+        shapes[p + "dwa"] = (i + 2,)
+        H = mix["heads"]
+        if layer["type"] == "hgrn2":
+            K, V = mix["dim"], mix["vdim"]
+            shapes.update({p + "mix.q": (H * K, D), p + "mix.f": (H * K, D), p + "mix.f.b": (H * K,), p + "mix.lower": (H * K,),
+                           p + "mix.v": (H * V, D), p + "mix.norm": (V,), p + "mix.o": (D, H * V)})
+        elif layer["type"] == "wkv":
+            K = mix["dim"]
+            for s in "rkvgw":
+                shapes[p + "mix.mu." + s] = (D,)
+            for s in "rkvg":
+                shapes[p + "mix." + s] = (H * K, D)
+            shapes.update({p + "mix.w1": (decay_rank, D), p + "mix.w2": (H * K, decay_rank), p + "mix.w0": (H * K,),
+                           p + "mix.u": (H, K), p + "mix.norm": (H * K,), p + "mix.o": (D, H * K)})
+        else:
+            K, R, V = mix["dim"], mix["rot_dim"], mix["vdim"]
+            shapes.update({p + "mix.dq": (mix["q_rank"], D), p + "mix.dq.norm": (mix["q_rank"],),
+                           p + "mix.uq": (H * (K + R), mix["q_rank"]), p + "mix.uk": (H * K, mix["kv_rank"]),
+                           p + "mix.uv": (H * V, mix["kv_rank"]), p + "mix.o": (D, H * V)})
+            if mix.get("kv_from") is None:
+                shapes.update({p + "mix.dkv": (mix["kv_rank"] + R, D), p + "mix.dkv.norm": (mix["kv_rank"],)})
+        if layer.get("mlp") is not None:
+            ff = layer["mlp"]["ff"]
+            shapes.update({p + "norm2": (D,), p + "ls2": (D,), p + "mlp.up": (ff, D), p + "mlp.down": (D, ff),
+                           p + "mlp.act": (2,)})
+    return shapes
+
+
+def random_weights(cfg, seed, decay_rank=16, gain=1.0):
+    """name -> bfloat16 tensor (what a model folder stores)."""
+    g = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=g)
+    ru = lambda *s: torch.rand(*s, generator=g)
+    out = {}
+    for name, shape in tensor_shapes(cfg, decay_rank).items():
+        leaf = name.split(".", 1)[1] if name.startswith("l") and name[1].isdigit() else name
+        if len(shape) == 2 and leaf != "mix.u":
+            t = rn(*shape) * (gain / math.sqrt(shape[1]))
+            if name == "embed":
+                t = rn(*shape)
+        elif leaf in ("norm1", "norm2", "mix.norm", "mix.dq.norm", "mix.dkv.norm") or name == "final.norm":
+            t = 1 + 0.2 * rn(*shape)
+        elif leaf in ("ls1", "ls2"):
+            t = 0.4 + 0.8 * ru(*shape)
+        elif leaf == "dwa":
+            t = (0.3 + ru(*shape))
+            t = t / t.sum() * (1 + 0.1 * rn(1))
+        elif leaf.startswith("mix.mu."):
+            t = ru(*shape)
+        elif leaf == "mix.w0":
+            t = rn(*shape) * 1.5 - 1.5            # decays from about 0.2 to nearly 1
+        elif leaf == "mix.u":
+            t = 0.5 * rn(*shape)
+        elif leaf == "mix.lower":
+            t = 0.95 * ru(*shape)
+        elif leaf == "mix.f.b":
+            t = rn(*shape)
+        elif leaf == "mlp.act":
+            t = 0.7 * rn(*shape)
+        else:
+            raise ValueError(name)
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+def greedy(cfg, weights, prompt, n_new, dtype=torch.float64):
+    """Greedy continuation by running the whole sequence anew for every token; returns (tokens, the margin
+    between the best and the second logit at every choice)."""
+    toks, margins = list(prompt), []
+    for _ in range(n_new):
+        top = torch.topk(forward(cfg, weights, toks, dtype)[-1], 2)
+        toks.append(int(top.indices[0]))
+        margins.append(float(top.values[0] - top.values[1]))
+    return toks[len(prompt):], margins
