@@ -440,8 +440,112 @@ def dense_products(torch, raw, tokens=2048):
     return {"tokens": tokens, "status": int(st.item()), "rows": rows}
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --design zusepel: the decoder with recurrent mixers and latent attention, beside the dense Qwen2 decoder of the
+# same width, depth and feed-forward width (the closest model this library has), both with random weights.
+def zusepel_config(width, ff, layers, vocab, window):
+    heads = width // 128
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 3 * width // 8, "kv_rank": width // 4,
+           "scale": (128 + 64) ** -0.5, "mask": {"size": window},
+           "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "fast": 32.0, "original": 4096, "slow": 1.0}}}
+    pattern = [{"type": "hgrn2", "mixer": {"heads": heads, "dim": 128, "vdim": 128}},
+               {"type": "wkv", "mixer": {"heads": width // 64, "dim": 64}},
+               {"type": "latent_attention", "mixer": dict(lat)},
+               {"type": "latent_attention", "mixer": dict(lat, kv_from=-1)}]
+    out = []
+    for i in range(layers):
+        layer = {"type": pattern[i % 4]["type"], "mixer": dict(pattern[i % 4]["mixer"]), "mlp": {"kind": "dense", "ff": ff}}
+        if layer["mixer"].get("kv_from") == -1:
+            layer["mixer"]["kv_from"] = i - 1
+        out.append(layer)
+    return {"architecture": "Zusepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+            "layers": out, "decay_ranks": {str(i): 64 for i in range(layers) if out[i]["type"] == "wkv"}}
+
+
+def dense_qwen2_config(width, ff, layers, vocab):
+    return dict(A27B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=width // 128,
+                num_key_value_heads=width // 128, head_dim=128, vocab_size=vocab, intermediate_size=ff,
+                mlp_only_layers=list(range(layers)), max_position_embeddings=8192)
+
+
+def measure_design(torch, raw, prefill_tokens, batches, context, steps, warmup):
+    """Prefill of one prompt and decode steps of a model with random weights: tokens per second, and device time
+    by kind of kernel for one eager prefill and one eager decode step (library products count with the kernel
+    that follows them)."""
+    import gc
+    import numpy as np
+    from esp_b200.config import config_from_dict
+    from esp_b200.csrc import ops
+    from esp_b200.engine import Engine, StepEntry
+    from esp_b200.weights import InitSpec
+    cfg = config_from_dict(raw)
+    top = max(batches)
+    engine = Engine.from_random(cfg, seed=0, init=InitSpec(0.02, 0.0, 0.0), dtype="bfloat16",
+                                max_tokens=top * (context + 64) + prefill_tokens + 64, max_slots=top + 2)
+    vocab = engine.plan.vocab
+    rng = np.random.default_rng(1)
+    out = {"weights_gb": round(engine.memory_plan["weights_bytes"] / 1e9, 2)}
+
+    def prefill_once():
+        s = engine.open()
+        engine.step([StepEntry(s, rng.integers(0, vocab, prefill_tokens).tolist(), [prefill_tokens - 1])])
+        engine.close(s)
+
+    ms = timed_steps(torch, prefill_once, max(3, warmup), max(4, steps // 4))
+    out["prefill"] = {"tokens": prefill_tokens, "ms": round(ms, 3), "tok_s": round(prefill_tokens / ms * 1e3, 1)}
+    launches = ops.launch_count()
+    for b in batches:
+        ms, _distinct, slots, _plen = decode_run(torch, engine, b, context, max(3, warmup), steps, vocab, seed=b)
+        out[f"decode_b{b}"] = {"ms": round(ms, 4), "tok_s": round(b / ms * 1e3, 1)}
+        for s in slots:
+            engine.close(s)
+    out["gpu_launches"] = ops.launch_count() - launches
+    # by kind of kernel
+    slot = engine.open()
+    toks = rng.integers(0, vocab, prefill_tokens).tolist()
+    for _ in range(2):
+        engine.close(slot)
+        slot = engine.open()
+        _lg, prof_p = engine.profile_step([StepEntry(slot, toks, [prefill_tokens - 1])])
+        _lg, prof_d = engine.profile_step([StepEntry(slot, [toks[-1]], [0])])
+    engine.close(slot)
+    out["prefill_by_kernel_us"] = {w: [n, round(us, 1)] for w, n, us in prof_p.rows()}
+    out["decode_by_kernel_us"] = {w: [n, round(us, 1)] for w, n, us in prof_d.rows()}
+    engine.raise_on_status()
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_design(torch, a, pk):
+    sizes = {"w1024": (1024, 2816, 8), "w2048": (2048, 5632, 8), "w4096": (4096, 11008, 8)}
+    picked = [s for s in a.design_sizes.split(",") if s]
+    vocab, window = 32768, 4096
+    result = {"design": "zusepel", "beside": "dense Qwen2 decoder of equal width, depth and feed-forward width", "dtype": "bf16",
+              "data": "synthetic token ids, random weights N(0,0.02)", "prefill_tokens": a.prefill_tokens,
+              "context": a.context, "steps": a.steps, "warmup": max(3, a.warmup), "peaks": pk, "sizes": {}}
+    clocks = ClockSampler()
+    with clocks:
+        for name in picked:
+            width, ff, layers = sizes[name]
+            entry = {"width": width, "ff": ff, "layers": layers, "vocab": vocab}
+            entry["zusepel"] = measure_design(torch, zusepel_config(width, ff, layers, vocab, window), a.prefill_tokens, (1, 8),
+                                              a.context, a.steps, a.warmup)
+            entry["qwen2_dense"] = measure_design(torch, dense_qwen2_config(width, ff, layers, vocab), a.prefill_tokens,
+                                                  (1, 8), a.context, a.steps, a.warmup)
+            result["sizes"][name] = entry
+    result["clocks"] = clocks.summary()
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default=None, choices=["zusepel"],
+                    help="instead of the default workload: prefill and decode of this design at a few layer sizes, beside "
+                         "the dense Qwen2 decoder of equal size")
+    ap.add_argument("--design-sizes", default="w1024,w2048", help="with --design: which of w1024, w2048, w4096")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
@@ -477,6 +581,10 @@ def main() -> int:
 
     pk = peaks()
     raw, shape_name = SHAPES[a.shape]
+    if a.design:
+        if a.context == 4096:
+            a.context = 2048
+        return bench_design(torch, a, pk)
     if a.dense_products:
         print(json.dumps({"model": shape_name, **dense_products(torch, raw)}))
         return 0
