@@ -34,7 +34,7 @@ LIBRARIES = {
     # that a model without such layers does not compile it
     "mixers": ["recurrent.cu", "latent.cu"],
     # bfloat16 only: loaded when a model runs in bfloat16
-    "bf16": ["gemm_skinny.cu", "attn_decode.cu", "attn_prefill.cu"],
+    "bf16": ["gemm_skinny.cu", "attn_decode.cu", "attn_prefill.cu", "attn_latent_mma.cu"],
     # TMA + tcgen05/TMEM products for steps with many rows (bfloat16 prefill)
     "tc05": ["gemm_tc05.cu", "attn_prefill_tc05.cu"],
 }

@@ -36,6 +36,8 @@ _SIGNATURES = {
                             P],
     "esp_latent_q_rotate": [P, P, c_float, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
     "esp_per_head_linear": [P, c_int, c_longlong, c_int, P, c_int, P, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, P],
+    "esp_attn_latent_mma": [P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_float, c_int, c_int, P, P, P, P],
     "esp_attn_latent": [P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P, P],
     "esp_swiglu": [P, P, c_int, c_longlong, c_int, P],
     "esp_finite_check": [P, c_int, c_longlong, P, c_int, P],
@@ -769,3 +771,38 @@ def attn_latent(qx, pool, out, tok_seq, tok_pos, block_table, page, heads, key_d
         _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(block_table, torch.int32), block_table.shape[1],
         pool.shape[0], page, qx.shape[0], heads, key_dim, value_dim, int(window or 0), float(scale),
         _ptr(status, torch.int32), _stream()), "attn_latent")
+
+
+ATTN_LATENT_MMA_ROWS = 32        # (token, head) rows of a tile of attn_latent_mma
+
+
+def attn_latent_mma_heads(heads: int) -> int:
+    """Heads of a tile: the power of two that holds all heads, at most the tile's rows."""
+    hg = 1
+    while hg < heads and hg < ATTN_LATENT_MMA_ROWS:
+        hg *= 2
+    return hg
+
+
+def attn_latent_mma_fits(key_dim: int, value_dim: int, page: int) -> bool:
+    smem = (2 * 64 + 32) * (key_dim + 8) * 2 + 32 * 72 * 2 + 8 * 32 * 4
+    return page == 64 and key_dim % 16 == 0 and value_dim % 16 == 0 and value_dim <= min(512, key_dim) and smem <= 227 * 1024
+
+
+def attn_latent_mma(qx, pool, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, heads, key_dim, value_dim,
+                    window, scale, status, n_splits=1, pages_per_split=0, part_o=None, part_ml=None):
+    """attn_latent on the tensor cores (bfloat16).  tile_seq / tile_first list tiles of 32 / attn_latent_mma_heads(heads)
+    new tokens of one sequence each.  n_splits > 1: the pages a tile sees are dealt to that many blocks,
+    pages_per_split each, through the float32 scratch part_o [rows, heads, n_splits, value_dim] and part_ml [rows, heads,
+    n_splits, 2]."""
+    if not attn_latent_mma_fits(key_dim, value_dim, page) or pool.shape[-1] != key_dim:
+        raise Backend(f"attn_latent_mma: rows of {key_dim} / values of {value_dim} channels / pages of {page} not taken")
+    n = qx.shape[0]
+    if n_splits > 1 and (part_o.numel() < n * heads * n_splits * value_dim or part_ml.numel() < n * heads * n_splits * 2):
+        raise Backend("attn_latent_mma: scratch is too small")
+    _check(_fn("bf16", "esp_attn_latent_mma")(
+        _ptr(qx, torch.bfloat16, "qx"), _ptr(pool, torch.bfloat16, "pool"), _ptr(out, torch.bfloat16, "out"),
+        _ptr(tile_seq, torch.int32), _ptr(tile_first, torch.int32), _ptr(seq_start, torch.int32), _ptr(seq_past, torch.int32),
+        _ptr(block_table, torch.int32), block_table.shape[1], pool.shape[0], page, tile_seq.shape[0], n, heads,
+        attn_latent_mma_heads(heads), key_dim, value_dim, int(window or 0), float(scale), int(n_splits), int(pages_per_split),
+        _ptr(part_o, torch.float32), _ptr(part_ml, torch.float32), _ptr(status, torch.int32), _stream()), "attn_latent_mma")

@@ -1,9 +1,11 @@
 """Attention through a cached low-rank latent, with a sliding window and a rotated key part shared by the heads."""
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache import KvLayout
+from ..cache.book import PAGE
 from ..csrc import ops
 from .base import ParamSpec, Part, build, register
 from .linear import linear
@@ -83,6 +85,50 @@ class LatentAttention(Part):
     def state_spec(self):
         return None
 
+    # -- which attention kernel a step gets, and the index lists it needs --------------
+    def _tensor_cores(self, page: int = PAGE) -> bool:
+        return self.rt.dtype == torch.bfloat16 and ops.attn_latent_mma_fits(self.row, self.spec.kv_rank, page)
+
+    def step_arrays_key(self):
+        return ("latent_attention", self.rt.dtype, ops.attn_latent_mma_heads(self.spec.num_heads)) if self._tensor_cores() else None
+
+    def step_arrays(self, step):
+        """Tiles of new tokens of one sequence for the tensor-core kernel: (sequence, first new token) per tile."""
+        if not self._tensor_cores():
+            return {}
+        tq = ops.ATTN_LATENT_MMA_ROWS // ops.attn_latent_mma_heads(self.spec.num_heads)
+        tiles = [(i, f) for i, t in enumerate(step.news) for f in range(0, t, tq)]
+        return {f"latent.tiles{tq}.seq": np.asarray([t[0] for t in tiles], dtype=np.int32),
+                f"latent.tiles{tq}.first": np.asarray([t[1] for t in tiles], dtype=np.int32)}
+
+    def attend(self, qx, o_lat, ctx, layer, table):
+        s, rt = self.spec, self.rt
+        H = s.num_heads
+        hg = ops.attn_latent_mma_heads(H)
+        tq = ops.ATTN_LATENT_MMA_ROWS // hg
+        tile_seq = ctx.arrays.get(f"latent.tiles{tq}.seq") if self._tensor_cores(layer.page) else None
+        if tile_seq is None:
+            ops.attn_latent(qx, layer.k, o_lat, ctx.tok_seq, ctx.tok_pos, table, layer.page, H, self.row, s.kv_rank, s.window,
+                            s.scale, rt.status)
+            return
+        tile_first = ctx.arrays[f"latent.tiles{tq}.first"]
+        # few blocks and many pages: deal every tile's pages to several blocks, so that the cache streams at full width
+        n = qx.shape[0]
+        blocks = tile_seq.shape[0] * ((H + hg - 1) // hg)
+        positions = table.shape[1] * layer.page
+        span = min(positions, s.window + tq + layer.page) if s.window else positions
+        pages = (span + layer.page - 1) // layer.page
+        n_splits = max(1, min(pages, (2 * rt.sm_count) // max(1, blocks)))
+        part_o = part_ml = None
+        per = 0
+        if n_splits > 1:
+            per = (pages + n_splits - 1) // n_splits
+            n_splits = (pages + per - 1) // per
+            part_o = rt.ws.get("la_part_o", (n, H, n_splits, s.kv_rank), torch.float32)
+            part_ml = rt.ws.get("la_part_ml", (n, H, n_splits, 2), torch.float32)
+        ops.attn_latent_mma(qx, layer.k, o_lat, tile_seq, tile_first, ctx.seq_start, ctx.seq_past, table, layer.page, H, self.row,
+                            s.kv_rank, s.window, s.scale, rt.status, n_splits, per, part_o, part_ml)
+
     def forward(self, h, ctx, layer):
         s, rt, pos = self.spec, self.rt, self.position
         n, H = h.shape[0], s.num_heads
@@ -104,8 +150,7 @@ class LatentAttention(Part):
         ops.per_head_linear(q, H * self.q_head, self.q_head, self.w_uk_t, qx, H * self.row, self.row, n, H, s.nope_dim,
                             s.kv_rank)
         o_lat = rt.ws.get("la_olat", (n, H * s.kv_rank), rt.dtype)
-        ops.attn_latent(qx, layer.k, o_lat, ctx.tok_seq, ctx.tok_pos, table, layer.page, H, self.row, s.kv_rank, s.window,
-                        s.scale, rt.status)
+        self.attend(qx, o_lat, ctx, layer, table)
         o = rt.ws.get("la_o", (n, H * s.value_dim), rt.dtype)
         ops.per_head_linear(o_lat, H * s.kv_rank, s.kv_rank, self.w_uv.view(H, s.value_dim, s.kv_rank), o, H * s.value_dim,
                             s.value_dim, n, H, s.kv_rank, s.value_dim)

@@ -320,3 +320,43 @@ def test_scaled_add_norm_depth_average_and_activation():
         act = torch.empty_like(z)
         ops.xielu(z, torch.tensor([p, q], device=DEV), act)
         assert float((act.double().cpu() - plain.xielu(z.double().cpu(), p, q)).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("H,hdk,hdv,window", [(6, 64, 48, 37), (1, 32, 16, 1), (13, 176, 144, 0), (3, 576, 512, 200),
+                                              (32, 96, 64, 136), (40, 96, 64, 70), (16, 320, 256, 100)])
+def test_attention_on_tensor_cores(H, hdk, hdv, window, splits):
+    """The tensor-core form against float64: runs of new tokens behind cached ones, a run of five first tokens, single
+    tokens, head counts that fill a tile, leave rows empty or need two tiles, with and without splitting the keys."""
+    torch.manual_seed(7 + H)
+    page = 64
+    perm = torch.randperm(9).tolist()
+    table = i32([perm[:5] + [-1, -1], perm[5:8] + [-1, -1, -1, -1], [perm[8]] + [-1] * 6])
+    lens, pasts = [290, 131, 5], [100, 130, 0]
+    rows = torch.randn(3, 300, hdk).to(torch.bfloat16)
+    pool = torch.zeros(9, 1, page, hdk, dtype=torch.bfloat16, device=DEV)
+    for s in range(3):
+        for j in range(lens[s]):
+            pool[int(table[s, j // page]), 0, j % page] = rows[s, j].to(DEV)
+    news = [lens[s] - pasts[s] for s in range(3)]
+    N = sum(news)
+    starts = np.concatenate([[0], np.cumsum(news)])
+    qx = (torch.randn(N, H * hdk) * 0.3).to(torch.bfloat16)
+    hg = ops.attn_latent_mma_heads(H)
+    tq = 32 // hg
+    tiles = [(s, f) for s in range(3) for f in range(0, news[s], tq)]
+    out = torch.zeros(N, H * hdv, dtype=torch.bfloat16, device=DEV)
+    st = status()
+    part_o = torch.empty(N, H, splits, hdv, device=DEV) if splits > 1 else None
+    part_ml = torch.empty(N, H, splits, 2, device=DEV) if splits > 1 else None
+    ops.attn_latent_mma(qx.to(DEV), pool, out, i32([t[0] for t in tiles]), i32([t[1] for t in tiles]), i32(starts), i32(pasts),
+                        table, page, H, hdk, hdv, window or None, 0.21, st, splits, 2, part_o, part_ml)
+    assert int(st.item()) == 0
+    worst = 0.0
+    for s in range(3):
+        for t in range(news[s]):
+            n = starts[s] + t
+            want = attention_reference(qx[n].double().view(H, hdk), rows[s].double(), pasts[s] + t, window, 0.21, hdv)
+            err = float((out[n].double().cpu().view(H, hdv) - want).abs().max()) / max(1.0, float(want.abs().max()))
+            worst = max(worst, err)
+            assert err <= 2 ** -6, (s, t, err)
