@@ -100,6 +100,7 @@ __global__ void latent_q_rotate_kernel(const float* __restrict__ q, const float*
 // A block takes ROWS rows of one head; a warp takes output channels in turn, its lanes the input channels, so a
 // weight row is read once per ROWS rows; sums run lane-wise in index order and then over a fixed butterfly.
 constexpr int PH_ROWS = 8;
+constexpr int PH_OUTS = 32;       // output channels of a block
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(128)
 per_head_linear_kernel(const TA* __restrict__ a, long long lda, int a_head, const TW* __restrict__ w, TO* __restrict__ out,
@@ -116,7 +117,8 @@ per_head_linear_kernel(const TA* __restrict__ a, long long lda, int a_head, cons
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const TW* wh = w + (size_t)h * nout * kin;
-    for (int j = warp; j < nout; j += 4) {
+    const int j_end = min(nout, ((int)blockIdx.z + 1) * PH_OUTS);
+    for (int j = blockIdx.z * PH_OUTS + warp; j < j_end; j += 4) {
         float acc[PH_ROWS];
 #pragma unroll
         for (int r = 0; r < PH_ROWS; r++) acc[r] = 0.f;
@@ -131,6 +133,99 @@ per_head_linear_kernel(const TA* __restrict__ a, long long lda, int a_head, cons
             if (lane == 0 && r < rows) out[(size_t)(n0 + r) * ldo + (size_t)h * o_head + j] = from_f32<TO>(s);
         }
     }
+}
+
+// The same product on the tensor cores for many rows and bfloat16 weights: a block takes 64 rows x 64 output channels
+// of one head, four warps 32 x 32 each, the input channels in pieces of 32 through shared memory (inputs are rounded
+// to bfloat16 as they are staged; sums are float).
+constexpr int PHM_MIN_ROWS = 17;
+constexpr int PHM_T = 64, PHM_KC = 32, PHM_LD = PHM_KC + 8;
+
+__device__ __forceinline__ void phm_ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void phm_mma(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TA, typename TO>
+__global__ void __launch_bounds__(128)
+per_head_mma_kernel(const TA* __restrict__ a, long long lda, int a_head, const bf16* __restrict__ w, TO* __restrict__ out,
+                    long long ldo, int o_head, int n_rows, int kin, int nout) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) bf16 as[PHM_T * PHM_LD];
+    __shared__ __align__(16) bf16 ws[PHM_T * PHM_LD];
+    const int n0 = blockIdx.x * PHM_T, h = blockIdx.y, j0 = blockIdx.z * PHM_T;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
+    const int wr = (warp & 1) * 32, wc = (warp >> 1) * 32;
+    const bf16* wh = w + (size_t)h * nout * kin;
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+#pragma unroll
+            for (int k = 0; k < 4; k++) acc[i][j][k] = 0.f;
+    for (int k0 = 0; k0 < kin; k0 += PHM_KC) {
+        __syncthreads();
+        for (int idx = tid; idx < PHM_T * PHM_KC; idx += 128) {
+            const int r = idx / PHM_KC, c = idx - r * PHM_KC;
+            const int k = k0 + c;
+            const bool kin_ok = k < kin;
+            as[r * PHM_LD + c] = (kin_ok && n0 + r < n_rows)
+                ? __float2bfloat16_rn(to_f32(a[(size_t)(n0 + r) * lda + (size_t)h * a_head + k])) : __float2bfloat16_rn(0.f);
+            ws[r * PHM_LD + c] = (kin_ok && j0 + r < nout) ? wh[(size_t)(j0 + r) * kin + k] : __float2bfloat16_rn(0.f);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < PHM_KC / 16; kk++) {
+            unsigned af[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++)
+                phm_ldmatrix_x4(af[mt], as + (wr + mt * 16 + (lane & 15)) * PHM_LD + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++) {
+                unsigned bfr[4];
+                phm_ldmatrix_x4(bfr, ws + (wc + nb * 16 + (lane & 7) + (lane >> 4) * 8) * PHM_LD + kk * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+                for (int mt = 0; mt < 2; mt++) {
+                    phm_mma(acc[mt][2 * nb], af[mt], bfr[0], bfr[1]);
+                    phm_mma(acc[mt][2 * nb + 1], af[mt], bfr[2], bfr[3]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int r = n0 + wr + mt * 16 + g + 8 * (e >> 1), j = j0 + wc + nt * 8 + tg * 2 + (e & 1);
+                if (r < n_rows && j < nout) out[(size_t)r * ldo + (size_t)h * o_head + j] = from_f32<TO>(acc[mt][nt][e]);
+            }
+}
+
+int launch_per_head_mma(const void* a, int a_dtype, long long lda, int a_head, const void* w, void* out, int o_dtype,
+                        long long ldo, int o_head, int n_rows, int H, int kin, int nout, cudaStream_t stream) {
+    dim3 grid((n_rows + PHM_T - 1) / PHM_T, H, (nout + PHM_T - 1) / PHM_T);
+#define ESP_PHM(TA, TO)                                                                                                     \
+    esp_launch_pdl(ESP_PDL_SMALL, per_head_mma_kernel<TA, TO>, grid, dim3(128), 0, stream, (const TA*)a, lda, a_head,         \
+                   (const bf16*)w, (TO*)out, ldo, o_head, n_rows, kin, nout)
+    switch (a_dtype * 2 + o_dtype) {
+        case 0: ESP_PHM(float, float); break;
+        case 1: ESP_PHM(float, bf16); break;
+        case 2: ESP_PHM(bf16, float); break;
+        default: ESP_PHM(bf16, bf16); break;
+    }
+#undef ESP_PHM
+    return esp_launch_status();
 }
 
 // ---------------------------------------------------------------------------------------------- attention
@@ -316,7 +411,9 @@ ESP_API int esp_per_head_linear(const void* a, int a_dtype, long long lda, int a
                                 cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H > 65535 || (size_t)PH_ROWS * kin * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
-    dim3 grid((n_rows + PH_ROWS - 1) / PH_ROWS, H);
+    if (w_dtype == 1 && n_rows >= PHM_MIN_ROWS)
+        return launch_per_head_mma(a, a_dtype, lda, a_head, w, out, o_dtype, ldo, o_head, n_rows, H, kin, nout, stream);
+    dim3 grid((n_rows + PH_ROWS - 1) / PH_ROWS, H, (nout + PH_OUTS - 1) / PH_OUTS);
     const size_t smem = (size_t)PH_ROWS * kin * sizeof(float);
 #define ESP_CASE(code_, TA, TW, TO)                                                                                          \
     case code_:                                                                                                             \

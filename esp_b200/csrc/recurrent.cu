@@ -73,6 +73,10 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src));
 }
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
 
@@ -87,7 +91,7 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
                   float* __restrict__ state, long long state_stride, const int* __restrict__ seq_start,
                   const int* __restrict__ seq_slot, float* __restrict__ out, int H, int K, int V, int ks, int vt) {
     pdl_trigger();
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int kp = ks * KT;                        // key channels, padded to the threads' slices
     // per buffer: q[CHUNK][kp], k[CHUNK][kp], d[CHUNK][kp], v[CHUNK][vt]
     const int buf_floats = CHUNK * (3 * kp + vt);
@@ -117,19 +121,40 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
 #pragma unroll
     for (int i = 0; i < KT; i++) S[i] = (live && part * KT + i < K) ? srow[i] : 0.f;
 
+    // 16-byte copies where every row piece is aligned (the usual case: K, V and the row strides multiples of 4)
+    const bool wide = (K % 4 == 0) && (V % 4 == 0) && (vt % 4 == 0) && (ldq % 4 == 0) && (ldg % 4 == 0) && (ldv % 4 == 0) &&
+                      (MODE != GATE_EXP_EXP || ldk % 4 == 0) && ((((size_t)q | (size_t)g | (size_t)v | (size_t)(MODE == GATE_EXP_EXP ? k : q)) & 15) == 0);
+    float bonus_r[KT];
+#pragma unroll
+    for (int i = 0; i < KT; i++) bonus_r[i] = c_bonus[part * KT + i];
     auto stage = [&](int buffer, int r0) {
         float* base = smem + buffer * buf_floats;
         const int count = min(CHUNK, row1 - r0);
-        for (int i = tid; i < count * K; i += SCAN_THREADS) {
-            const int t = i / K, c = i - t * K;
-            const size_t r = (size_t)(r0 + t);
-            cp_async4(base + t * kp + c, q + r * ldq + h * K + c);
-            if (MODE == GATE_EXP_EXP) cp_async4(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
-            cp_async4(base + (2 * CHUNK + t) * kp + c, g + r * ldg + h * K + c);
-        }
-        for (int i = tid; i < count * vt; i += SCAN_THREADS) {
-            const int t = i / vt, c = i - t * vt;
-            if (v0 + c < V) cp_async4(base + 3 * CHUNK * kp + t * vt + c, v + (size_t)(r0 + t) * ldv + h * V + v0 + c);
+        if (wide) {
+            const int k4 = K / 4, v4 = vt / 4;
+            for (int i = tid; i < count * k4; i += SCAN_THREADS) {
+                const int t = i / k4, c = (i - t * k4) * 4;
+                const size_t r = (size_t)(r0 + t);
+                cp_async16(base + t * kp + c, q + r * ldq + h * K + c);
+                if (MODE == GATE_EXP_EXP) cp_async16(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
+                cp_async16(base + (2 * CHUNK + t) * kp + c, g + r * ldg + h * K + c);
+            }
+            for (int i = tid; i < count * v4; i += SCAN_THREADS) {
+                const int t = i / v4, c = (i - t * v4) * 4;
+                if (v0 + c < V) cp_async16(base + 3 * CHUNK * kp + t * vt + c, v + (size_t)(r0 + t) * ldv + h * V + v0 + c);
+            }
+        } else {
+            for (int i = tid; i < count * K; i += SCAN_THREADS) {
+                const int t = i / K, c = i - t * K;
+                const size_t r = (size_t)(r0 + t);
+                cp_async4(base + t * kp + c, q + r * ldq + h * K + c);
+                if (MODE == GATE_EXP_EXP) cp_async4(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
+                cp_async4(base + (2 * CHUNK + t) * kp + c, g + r * ldg + h * K + c);
+            }
+            for (int i = tid; i < count * vt; i += SCAN_THREADS) {
+                const int t = i / vt, c = i - t * vt;
+                if (v0 + c < V) cp_async4(base + 3 * CHUNK * kp + t * vt + c, v + (size_t)(r0 + t) * ldv + h * V + v0 + c);
+            }
         }
         cp_async_commit();
     };
@@ -160,18 +185,26 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
         }
         __syncthreads();
         for (int t = 0; t < count; t++) {
-            const float* tq = sq + t * kp + part * KT, *tk = sk + t * kp + part * KT, *td = sd + t * kp + part * KT;
+            const float4* tq = reinterpret_cast<const float4*>(sq + t * kp + part * KT);
+            const float4* tk = reinterpret_cast<const float4*>(sk + t * kp + part * KT);
+            const float4* td = reinterpret_cast<const float4*>(sd + t * kp + part * KT);
             const float vv = live ? sv[t * vt + col] : 0.f;
             float o = 0.f;
 #pragma unroll
-            for (int i = 0; i < KT; i++) {
-                const float a = tk[i] * vv;
-                if (MODE == GATE_EXP_EXP) {
-                    o = fmaf(tq[i], fmaf(c_bonus[part * KT + i], a, S[i]), o);
-                    S[i] = fmaf(td[i], S[i], a);
-                } else {
-                    S[i] = fmaf(td[i], S[i], a);
-                    o = fmaf(tq[i], S[i], o);
+            for (int i4 = 0; i4 < KT / 4; i4++) {
+                const float4 q4 = tq[i4], k4 = tk[i4], d4 = td[i4];
+                const float qe[4] = {q4.x, q4.y, q4.z, q4.w}, ke[4] = {k4.x, k4.y, k4.z, k4.w}, de[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int i = 4 * i4 + e;
+                    const float a = ke[e] * vv;
+                    if (MODE == GATE_EXP_EXP) {
+                        o = fmaf(qe[e], fmaf(bonus_r[i], a, S[i]), o);
+                        S[i] = fmaf(de[e], S[i], a);
+                    } else {
+                        S[i] = fmaf(de[e], S[i], a);
+                        o = fmaf(qe[e], S[i], o);
+                    }
                 }
             }
             for (int off = 1; off < ks; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
