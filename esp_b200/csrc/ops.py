@@ -29,7 +29,8 @@ _SIGNATURES = {
     "esp_tanh": [P, P, c_int, c_longlong, P],
     "esp_token_shift_mix": [P, c_int, P, c_longlong, P, P, P, P, P, c_int, c_int, c_int, P],
     "esp_token_shift_keep": [P, c_int, P, c_longlong, P, P, c_int, c_int, P],
-    "esp_gated_scan": [c_int, P, c_longlong, P, c_longlong, P, c_longlong, P, c_longlong, P, P, P, P, c_longlong, P, P, P,
+    "esp_gate_prepare": [c_int, P, c_longlong, P, c_longlong, P, P, P, P, P, c_longlong, c_int, P],
+    "esp_gated_scan": [c_int, c_int, P, c_longlong, P, c_longlong, P, c_longlong, P, c_longlong, P, P, P, P, c_longlong, P, P, P,
                        c_int, c_int, c_int, c_int, P],
     "esp_head_rmsnorm_gate": [P, P, c_int, P, c_longlong, P, c_int, c_int, c_int, c_int, c_float, P],
     "esp_latent_kv_store": [P, P, P, c_float, c_int, P, P, P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_float, P,
@@ -699,18 +700,31 @@ SCAN_LOWER_SIGMOID = 1        # d = lower + (1 - lower) sigmoid(g + bias), k = 1
 SCAN_MAX_KEY_DIM = 128
 
 
-def gated_scan(mode, q, k, g, v, gate_bias, lower, bonus, state, seq_start, seq_slot, out, n_seqs, heads, key_dim, value_dim):
+def gate_prepare(mode, q, g, gate_bias, lower, q_out, k_out, d_out):
+    """The gates of many rows ahead of ``gated_scan(..., ready=True)``: d_out (and for SCAN_LOWER_SIGMOID q_out = silu(q)
+    and k_out = 1 - d), float32 [rows, heads * key_dim], from the projections' raw outputs.  The same operations as
+    the recurrence applies when it makes the gates itself: equal bits."""
+    (pq, ldq), (pg, ldg) = _rows_ld(q, "q"), _rows_ld(g, "g")
+    _check(_fn("mixers", "esp_gate_prepare")(
+        int(mode), pq, ldq, pg, ldg, _ptr(gate_bias, torch.float32, "gate_bias"), _ptr(lower, torch.float32, "lower"),
+        _ptr(q_out, torch.float32, "q_out"), _ptr(k_out, torch.float32, "k_out"), _ptr(d_out, torch.float32, "d_out"),
+        g.shape[0], g.shape[1], _stream()), "gate_prepare")
+
+
+def gated_scan(mode, q, k, g, v, gate_bias, lower, bonus, state, seq_start, seq_slot, out, n_seqs, heads, key_dim, value_dim,
+               ready=False):
     """The gated outer-product recurrence S_t = diag(d_t) S_(t-1) + k_t v_t^T per head with its output, over the
     runs of rows that the sequences bring (seq_start), from and to ``state`` (float32 [slots, >= heads * value_dim *
     key_dim], a head's block laid out [value_dim, key_dim]).  q, k, g: float32 [rows, heads * key_dim]; v: float32
-    [rows, heads * value_dim]; out: float32 [rows, heads * value_dim].  All 32-bit."""
+    [rows, heads * value_dim]; out: float32 [rows, heads * value_dim].  All 32-bit.  ``ready``: q, k and g hold the
+    query, the written key and the decay themselves (``gate_prepare`` made them)."""
     if key_dim > SCAN_MAX_KEY_DIM:
         raise Backend(f"gated_scan: {key_dim} key channels per head are beyond the {SCAN_MAX_KEY_DIM} this kernel takes")
     if state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] < heads * key_dim * value_dim:
         raise Backend("gated_scan: the state rows are too short or not float32")
     (pq, ldq), (pk, ldk), (pg, ldg), (pv, ldv) = (_rows_ld(t, n) for t, n in ((q, "q"), (k, "k"), (g, "g"), (v, "v")))
     _check(_fn("mixers", "esp_gated_scan")(
-        int(mode), pq, ldq, pk, ldk, pg, ldg, pv, ldv, _ptr(gate_bias, torch.float32, "gate_bias"),
+        int(mode), 1 if ready else 0, pq, ldq, pk, ldk, pg, ldg, pv, ldv, _ptr(gate_bias, torch.float32, "gate_bias"),
         _ptr(lower, torch.float32, "lower"), _ptr(bonus, torch.float32, "bonus"), state.data_ptr(), state.stride(0),
         _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(out, torch.float32, "out"), int(n_seqs), heads,
         key_dim, value_dim, _stream()), "gated_scan")

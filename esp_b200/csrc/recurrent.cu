@@ -69,6 +69,13 @@ enum : int {
     GATE_LOWER_SIGMOID = 1 // d = lower + (1 - lower) * sigmoid(g + bias);  k = 1 - d;  q = silu(q);  o reads S_t
 };
 
+// The gates, written with explicit operations so that the kernel that makes them ahead of the recurrence and the
+// recurrence itself (when it makes them as it stages rows) give the same bits.
+__device__ __forceinline__ float gate_decay(float raw) { return expf(-expf(raw)); }
+__device__ __forceinline__ float gate_sigmoid(float raw) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-raw))); }
+__device__ __forceinline__ float gate_lower(float raw, float lo) { return __fmaf_rn(__fsub_rn(1.0f, lo), gate_sigmoid(raw), lo); }
+__device__ __forceinline__ float gate_silu(float z) { return __fmul_rn(z, gate_sigmoid(z)); }
+
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src));
@@ -83,7 +90,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 // q, k, g: [rows, ld*] float (k may be null in GATE_LOWER_SIGMOID); v: [rows, ldv]; head h reads columns
 // [h*K, (h+1)*K) (v: [h*V, (h+1)*V)).  state: [slots, state_stride] floats, the head's block at h*V*K laid out
 // [V][K] (a thread's key slice is contiguous).  out: [rows, H*V] float.
-template <int MODE>
+template <int MODE, bool READY>
 __global__ void __launch_bounds__(SCAN_THREADS)
 gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
                   const float* __restrict__ g, long long ldg, const float* __restrict__ v, long long ldv,
@@ -123,7 +130,8 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
 
     // 16-byte copies where every row piece is aligned (the usual case: K, V and the row strides multiples of 4)
     const bool wide = (K % 4 == 0) && (V % 4 == 0) && (vt % 4 == 0) && (ldq % 4 == 0) && (ldg % 4 == 0) && (ldv % 4 == 0) &&
-                      (MODE != GATE_EXP_EXP || ldk % 4 == 0) && ((((size_t)q | (size_t)g | (size_t)v | (size_t)(MODE == GATE_EXP_EXP ? k : q)) & 15) == 0);
+                      (!(MODE == GATE_EXP_EXP || READY) || ldk % 4 == 0) &&
+                      ((((size_t)q | (size_t)g | (size_t)v | (size_t)((MODE == GATE_EXP_EXP || READY) ? k : q)) & 15) == 0);
     float bonus_r[KT];
 #pragma unroll
     for (int i = 0; i < KT; i++) bonus_r[i] = c_bonus[part * KT + i];
@@ -136,7 +144,7 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
                 const int t = i / k4, c = (i - t * k4) * 4;
                 const size_t r = (size_t)(r0 + t);
                 cp_async16(base + t * kp + c, q + r * ldq + h * K + c);
-                if (MODE == GATE_EXP_EXP) cp_async16(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
+                if (MODE == GATE_EXP_EXP || READY) cp_async16(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
                 cp_async16(base + (2 * CHUNK + t) * kp + c, g + r * ldg + h * K + c);
             }
             for (int i = tid; i < count * v4; i += SCAN_THREADS) {
@@ -148,7 +156,7 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
                 const int t = i / K, c = i - t * K;
                 const size_t r = (size_t)(r0 + t);
                 cp_async4(base + t * kp + c, q + r * ldq + h * K + c);
-                if (MODE == GATE_EXP_EXP) cp_async4(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
+                if (MODE == GATE_EXP_EXP || READY) cp_async4(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
                 cp_async4(base + (2 * CHUNK + t) * kp + c, g + r * ldg + h * K + c);
             }
             for (int i = tid; i < count * vt; i += SCAN_THREADS) {
@@ -168,28 +176,29 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
         if (r0 + CHUNK < row1) stage(buffer ^ 1, r0 + CHUNK);
         float* base = smem + buffer * buf_floats;
         float* sq = base, *sk = base + CHUNK * kp, *sd = base + 2 * CHUNK * kp, *sv = base + 3 * CHUNK * kp;
-        // gates, in place
-        for (int i = tid; i < count * K; i += SCAN_THREADS) {
-            const int t = i / K, c = i - t * K;
-            const float raw = sd[t * kp + c] + c_bias[c];
-            if (MODE == GATE_EXP_EXP) {
-                sd[t * kp + c] = expf(-expf(raw));
-            } else {
-                const float lo = c_lower[c];
-                const float d = lo + (1.0f - lo) * (1.0f / (1.0f + expf(-raw)));
-                sd[t * kp + c] = d;
-                sk[t * kp + c] = 1.0f - d;
-                const float z = sq[t * kp + c];
-                sq[t * kp + c] = z / (1.0f + expf(-z));
+        if (!READY) {
+            // gates, in place
+            for (int i = tid; i < count * K; i += SCAN_THREADS) {
+                const int t = i / K, c = i - t * K;
+                const float raw = __fadd_rn(sd[t * kp + c], c_bias[c]);
+                if (MODE == GATE_EXP_EXP) {
+                    sd[t * kp + c] = gate_decay(raw);
+                } else {
+                    const float d = gate_lower(raw, c_lower[c]);
+                    sd[t * kp + c] = d;
+                    sk[t * kp + c] = __fsub_rn(1.0f, d);
+                    sq[t * kp + c] = gate_silu(sq[t * kp + c]);
+                }
             }
+            __syncthreads();
         }
-        __syncthreads();
+#pragma unroll 4
         for (int t = 0; t < count; t++) {
             const float4* tq = reinterpret_cast<const float4*>(sq + t * kp + part * KT);
             const float4* tk = reinterpret_cast<const float4*>(sk + t * kp + part * KT);
             const float4* td = reinterpret_cast<const float4*>(sd + t * kp + part * KT);
             const float vv = live ? sv[t * vt + col] : 0.f;
-            float o = 0.f;
+            float oe[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i4 = 0; i4 < KT / 4; i4++) {
                 const float4 q4 = tq[i4], k4 = tk[i4], d4 = td[i4];
@@ -199,14 +208,15 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
                     const int i = 4 * i4 + e;
                     const float a = ke[e] * vv;
                     if (MODE == GATE_EXP_EXP) {
-                        o = fmaf(qe[e], fmaf(bonus_r[i], a, S[i]), o);
+                        oe[e] = fmaf(qe[e], fmaf(bonus_r[i], a, S[i]), oe[e]);
                         S[i] = fmaf(de[e], S[i], a);
                     } else {
                         S[i] = fmaf(de[e], S[i], a);
-                        o = fmaf(qe[e], S[i], o);
+                        oe[e] = fmaf(qe[e], S[i], oe[e]);
                     }
                 }
             }
+            float o = (oe[0] + oe[1]) + (oe[2] + oe[3]);
             for (int off = 1; off < ks; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
             if (live && part == 0) out[(size_t)(r0 + t) * H * V + h * V + vcol] = o;
         }
@@ -215,6 +225,31 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
 #pragma unroll
         for (int i = 0; i < KT; i++)
             if (part * KT + i < K) srow[i] = S[i];
+    }
+}
+
+// The gates of many rows ahead of the recurrence (the recurrence itself is a chain over the tokens; this is not).
+// MODE 0: d = exp(-exp(g + bias)).  MODE 1: d = lower + (1 - lower) sigmoid(g + bias), k = 1 - d, q = silu(q).
+template <int MODE>
+__global__ void gate_prepare_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ g, long long ldg,
+                                    const float* __restrict__ gate_bias, const float* __restrict__ lower,
+                                    float* __restrict__ q_out, float* __restrict__ k_out, float* __restrict__ d_out,
+                                    long long rows, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = rows * width;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+        const long long r = idx / width;
+        const int c = (int)(idx - r * width);
+        const float raw = __fadd_rn(g[r * ldg + c], gate_bias ? gate_bias[c] : 0.f);
+        if (MODE == GATE_EXP_EXP) {
+            d_out[idx] = gate_decay(raw);
+        } else {
+            const float d = gate_lower(raw, lower ? lower[c] : 0.f);
+            d_out[idx] = d;
+            k_out[idx] = __fsub_rn(1.0f, d);
+            q_out[idx] = gate_silu(q[r * ldq + c]);
+        }
     }
 }
 
@@ -272,8 +307,28 @@ ESP_API int esp_token_shift_keep(const void* h, int is_bf16, float* prev_state, 
     return esp_launch_status();
 }
 
+// Makes the gates of ``rows`` rows ahead of esp_gated_scan(..., ready = 1): d_out (and, mode 1, q_out and k_out), each
+// float [rows, width] with width = heads * key channels.
+ESP_API int esp_gate_prepare(int mode, const float* q, long long ldq, const float* g, long long ldg, const float* gate_bias,
+                             const float* lower, float* q_out, float* k_out, float* d_out, long long rows, int width,
+                             cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    long long blocks = (rows * width + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (mode == GATE_EXP_EXP)
+        esp_launch_pdl(ESP_PDL_SMALL, gate_prepare_kernel<GATE_EXP_EXP>, dim3((int)blocks), dim3(256), 0, stream, q, ldq, g, ldg,
+                       gate_bias, lower, q_out, k_out, d_out, rows, width);
+    else if (mode == GATE_LOWER_SIGMOID && q && q_out && k_out)
+        esp_launch_pdl(ESP_PDL_SMALL, gate_prepare_kernel<GATE_LOWER_SIGMOID>, dim3((int)blocks), dim3(256), 0, stream, q, ldq, g,
+                       ldg, gate_bias, lower, q_out, k_out, d_out, rows, width);
+    else
+        return (int)cudaErrorInvalidValue;
+    return esp_launch_status();
+}
+
 // mode: 0 = decay exp(-exp(.)) with a bonus for the current token, 1 = lower-bounded sigmoid gate that also writes.
-ESP_API int esp_gated_scan(int mode, const float* q, long long ldq, const float* k, long long ldk, const float* g,
+// ready: q, k and g already hold the query, the written key and the decay (esp_gate_prepare made them).
+ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, const float* k, long long ldk, const float* g,
                            long long ldg, const float* v, long long ldv, const float* gate_bias, const float* lower,
                            const float* bonus, float* state, long long state_stride, const int* seq_start,
                            const int* seq_slot, float* out, int n_seqs, int H, int K, int V, cudaStream_t stream) {
@@ -286,21 +341,21 @@ ESP_API int esp_gated_scan(int mode, const float* q, long long ldq, const float*
     const int vtiles = (V + vt - 1) / vt;
     const size_t smem = 2 * (size_t)CHUNK * (3 * ks * KT + vt) * sizeof(float);
     dim3 grid(n_seqs, H, vtiles);
-    if (mode == GATE_EXP_EXP) {
-        if (!k) return (int)cudaErrorInvalidValue;
-        static bool set0 = false;
-        if (!set0) { cudaFuncSetAttribute(gated_scan_kernel<GATE_EXP_EXP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set0 = true; }
-        esp_launch_pdl(ESP_PDL_SMALL, gated_scan_kernel<GATE_EXP_EXP>, grid, dim3(SCAN_THREADS), smem, stream, q, ldq, k, ldk,
-                       g, ldg, v, ldv, gate_bias, lower, bonus, state, state_stride, seq_start, seq_slot, out, H, K, V, ks, vt);
-    } else if (mode == GATE_LOWER_SIGMOID) {
-        static bool set1 = false;
-        if (!set1) { cudaFuncSetAttribute(gated_scan_kernel<GATE_LOWER_SIGMOID>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set1 = true; }
-        esp_launch_pdl(ESP_PDL_SMALL, gated_scan_kernel<GATE_LOWER_SIGMOID>, grid, dim3(SCAN_THREADS), smem, stream, q, ldq, k,
-                       ldk, g, ldg, v, ldv, gate_bias, lower, bonus, state, state_stride, seq_start, seq_slot, out, H, K, V,
-                       ks, vt);
-    } else {
-        return (int)cudaErrorInvalidValue;
+    if ((mode == GATE_EXP_EXP || ready) && !k) return (int)cudaErrorInvalidValue;
+#define ESP_SCAN(MODE_, READY_)                                                                                              \
+    {                                                                                                                       \
+        auto kernel = gated_scan_kernel<MODE_, READY_>;                                                                     \
+        static bool set = false;                                                                                            \
+        if (!set) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set = true; }      \
+        esp_launch_pdl(ESP_PDL_SMALL, kernel, grid, dim3(SCAN_THREADS), smem, stream, q, ldq, k, ldk, g, ldg, v, ldv,         \
+                       gate_bias, lower, bonus, state, state_stride, seq_start, seq_slot, out, H, K, V, ks, vt);            \
     }
+    if (mode == GATE_EXP_EXP && !ready) ESP_SCAN(GATE_EXP_EXP, false)
+    else if (mode == GATE_EXP_EXP) ESP_SCAN(GATE_EXP_EXP, true)
+    else if (mode == GATE_LOWER_SIGMOID && !ready) ESP_SCAN(GATE_LOWER_SIGMOID, false)
+    else if (mode == GATE_LOWER_SIGMOID) ESP_SCAN(GATE_LOWER_SIGMOID, true)
+    else return (int)cudaErrorInvalidValue;
+#undef ESP_SCAN
     return esp_launch_status();
 }
 

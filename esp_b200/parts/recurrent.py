@@ -13,6 +13,11 @@ from .base import ParamSpec, Part, register
 from .linear import linear
 
 
+# Steps with more rows than this per sequence make the gates in a parallel pass ahead of the recurrence; shorter
+# ones (decoding) let the recurrence make them as it stages its rows.  Both give the same bits.
+GATES_AHEAD_ROWS = 8
+
+
 def _check_dims(kind, key_dim):
     if key_dim > ops.SCAN_MAX_KEY_DIM:
         raise Unsupported(kind + ".dim", f"{key_dim}; the recurrence kernel takes up to {ops.SCAN_MAX_KEY_DIM} key "
@@ -70,9 +75,15 @@ class LowerBoundRecurrence(Part):
         proj = rt.ws.get("rec_proj", (n, 2 * self.kw + self.vw), torch.float32)
         linear(rt, h, self.w_qfv, proj)
         o = rt.ws.get("rec_out", (n, self.vw), torch.float32)
-        ops.gated_scan(ops.SCAN_LOWER_SIGMOID, proj[:, :self.kw], None, proj[:, self.kw:2 * self.kw], proj[:, 2 * self.kw:],
-                       self.f_bias, self.lower, None, layer.state, ctx.seq_start, ctx.seq_slot, o, ctx.n_seqs,
-                       s.num_heads, s.key_dim, s.value_dim)
+        q, f, v = proj[:, :self.kw], proj[:, self.kw:2 * self.kw], proj[:, 2 * self.kw:]
+        if n > GATES_AHEAD_ROWS * ctx.n_seqs:
+            gates = rt.ws.get("rec_gates", (3, n, self.kw), torch.float32)
+            ops.gate_prepare(ops.SCAN_LOWER_SIGMOID, q, f, self.f_bias, self.lower, gates[0], gates[1], gates[2])
+            ops.gated_scan(ops.SCAN_LOWER_SIGMOID, gates[0], gates[1], gates[2], v, None, None, None, layer.state,
+                           ctx.seq_start, ctx.seq_slot, o, ctx.n_seqs, s.num_heads, s.key_dim, s.value_dim, ready=True)
+        else:
+            ops.gated_scan(ops.SCAN_LOWER_SIGMOID, q, None, f, v, self.f_bias, self.lower, None, layer.state, ctx.seq_start,
+                           ctx.seq_slot, o, ctx.n_seqs, s.num_heads, s.key_dim, s.value_dim)
         y = rt.ws.get("rec_normed", (n, self.vw), rt.dtype)
         ops.head_rmsnorm_gate(o, self.norm_w, 0, None, y, s.num_heads, s.value_dim, s.eps)
         out = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
@@ -153,8 +164,12 @@ class DecayBonusRecurrence(Part):
         ops.tanh(inner, inner_act)
         linear(rt, inner_act, self.w2, proj[4])
         o = rt.ws.get("rec_out", (n, self.kw), torch.float32)
-        ops.gated_scan(ops.SCAN_DECAY_BONUS, proj[0], proj[1], proj[4], proj[2], self.w0, None, self.u.view(-1), layer.state,
-                       ctx.seq_start, ctx.seq_slot, o, ctx.n_seqs, s.num_heads, s.head_dim, s.head_dim)
+        decay, ready = proj[4], False
+        if n > GATES_AHEAD_ROWS * ctx.n_seqs:
+            decay, ready = rt.ws.get("rec_gates", (1, n, self.kw), torch.float32)[0], True
+            ops.gate_prepare(ops.SCAN_DECAY_BONUS, None, proj[4], self.w0, None, None, None, decay)
+        ops.gated_scan(ops.SCAN_DECAY_BONUS, proj[0], proj[1], decay, proj[2], None if ready else self.w0, None, self.u.view(-1),
+                       layer.state, ctx.seq_start, ctx.seq_slot, o, ctx.n_seqs, s.num_heads, s.head_dim, s.head_dim, ready=ready)
         y = rt.ws.get("rec_normed", (n, self.kw), rt.dtype)
         ops.head_rmsnorm_gate(o, self.norm_w, s.head_dim, proj[3], y, s.num_heads, s.head_dim, s.eps)
         out = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)

@@ -360,3 +360,31 @@ def test_attention_on_tensor_cores(H, hdk, hdv, window, splits):
             err = float((out[n].double().cpu().view(H, hdv) - want).abs().max()) / max(1.0, float(want.abs().max()))
             worst = max(worst, err)
             assert err <= 2 ** -6, (s, t, err)
+
+
+@pytest.mark.parametrize("mode", [ops.SCAN_DECAY_BONUS, ops.SCAN_LOWER_SIGMOID])
+def test_gates_made_ahead_give_the_same_bits(mode):
+    torch.manual_seed(8)
+    H, K, V, T = 3, 48, 40, 70
+    q, k, g = (torch.randn(T, H * K, device=DEV) for _ in range(3))
+    v = torch.randn(T, H * V, device=DEV)
+    bias, lower, bonus = torch.randn(H * K, device=DEV), torch.rand(H * K, device=DEV), torch.randn(H * K, device=DEV)
+    outs, states = [], []
+    for ahead in (False, True):
+        state = torch.zeros(2, H * K * V, device=DEV)
+        out = torch.zeros(T, H * V, device=DEV)
+        if ahead:
+            made = torch.zeros(3, T, H * K, device=DEV)
+            if mode == ops.SCAN_DECAY_BONUS:
+                ops.gate_prepare(mode, None, g, bias, None, None, None, made[2])
+                ops.gated_scan(mode, q, k, made[2], v, None, None, bonus, state, i32([0, T]), i32([1]), out, 1, H, K, V, ready=True)
+            else:
+                ops.gate_prepare(mode, q, g, bias, lower, made[0], made[1], made[2])
+                ops.gated_scan(mode, made[0], made[1], made[2], v, None, None, None, state, i32([0, T]), i32([1]), out, 1, H, K, V,
+                               ready=True)
+        else:
+            ops.gated_scan(mode, q, k if mode == ops.SCAN_DECAY_BONUS else None, g, v, bias, lower if mode else None,
+                           bonus if not mode else None, state, i32([0, T]), i32([1]), out, 1, H, K, V)
+        outs.append(out)
+        states.append(state)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(states[0], states[1])
