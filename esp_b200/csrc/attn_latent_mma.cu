@@ -277,25 +277,42 @@ attn_latent_mma_kernel(const bf16* __restrict__ qx, const bf16* __restrict__ poo
 }
 
 // out[n, h] = sum_s w_s O_s / sum_s w_s l_s with w_s = exp(m_s - max m), splits added in ascending order.  A warp a row.
-__global__ void attn_latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           bf16* __restrict__ out, int rows, int n_splits, int hdv) {
+__global__ void __launch_bounds__(256)
+attn_latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, int rows,
+                           int n_splits, int hdv) {
     pdl_trigger();
     pdl_wait();
-    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    extern __shared__ float wts[];                  // [warps of the block][n_splits]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
     if (row >= rows) return;
+    float* w = wts + warp * n_splits;
     const float* ml = part_ml + (size_t)row * n_splits * 2;
     float m = -INFINITY;
-    for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
+    for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, ml[2 * s]);
+    m = warp_max(m);
+    for (int s = lane; s < n_splits; s += 32) w[s] = ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - m);
+    __syncwarp();
     float l = 0.f;
-    for (int s = 0; s < n_splits; s++) l += ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - m) * ml[2 * s + 1];
+    for (int s = 0; s < n_splits; s++) l = fmaf(w[s], ml[2 * s + 1], l);
     const float inv = l > 0.f ? 1.0f / l : 0.f;
-    for (int c = lane; c < hdv; c += 32) {
-        float acc = 0.f;
+    const float* po = part_o + (size_t)row * n_splits * hdv;
+    for (int c0 = 0; c0 < hdv; c0 += 128) {         // four channels a lane, every split's piece one 16-byte load
+        const int c = c0 + lane * 4;
+        if (c >= hdv) continue;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
         for (int s = 0; s < n_splits; s++) {
-            if (ml[2 * s] == -INFINITY) continue;
-            acc = fmaf(expf(ml[2 * s] - m), part_o[((size_t)row * n_splits + s) * hdv + c], acc);
+            const float4 v = *reinterpret_cast<const float4*>(po + (size_t)s * hdv + c);
+            const float ws = w[s];
+            acc.x = fmaf(ws, v.x, acc.x);
+            acc.y = fmaf(ws, v.y, acc.y);
+            acc.z = fmaf(ws, v.z, acc.z);
+            acc.w = fmaf(ws, v.w, acc.w);
         }
-        out[(size_t)row * hdv + c] = __float2bfloat16_rn(acc * inv);
+        bf16* dst = out + (size_t)row * hdv + c;
+        *reinterpret_cast<unsigned*>(dst) = pack_bf16(acc.x * inv, acc.y * inv);
+        *reinterpret_cast<unsigned*>(dst + 2) = pack_bf16(acc.z * inv, acc.w * inv);
     }
 }
 
@@ -310,7 +327,8 @@ int launch(const void* qx, const void* pool, void* out, const int* tile_seq, con
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); set = true; }
     dim3 grid(n_tiles, (H + hg - 1) / hg, n_splits);
-    esp_launch_pdl(ESP_PDL_ATTENTION, kernel, grid, dim3(THREADS), smem, stream, (const bf16*)qx, (const bf16*)pool, (bf16*)out,
+    // many tiles: a long kernel that fills the device, launched the ordinary way; few (decoding): set up under its predecessor
+    esp_launch_pdl(n_tiles > 64 ? 0 : ESP_PDL_ATTENTION, kernel, grid, dim3(THREADS), smem, stream, (const bf16*)qx, (const bf16*)pool, (bf16*)out,
                    tile_seq, tile_first, seq_start, seq_past, block_table, table_stride, n_pages, H, hg, hdk, hdv, window, scale,
                    n_splits, pages_per_split, part_o, part_ml, status);
     return esp_launch_status();
@@ -342,7 +360,9 @@ ESP_API int esp_attn_latent_mma(const void* qx, const void* pool, void* out, con
 #undef ESP_GO
     if (code != 0 || n_splits == 1) return code;
     const long long rows = (long long)n_rows * H;
-    esp_launch_pdl(ESP_PDL_ATTENTION, attn_latent_combine_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, stream,
+    if ((size_t)8 * n_splits * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+    esp_launch_pdl(ESP_PDL_ATTENTION, attn_latent_combine_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256),
+                   (size_t)8 * n_splits * sizeof(float), stream,
                    (const float*)part_o, (const float*)part_ml, (bf16*)out, (int)rows, n_splits, hdv);
     return esp_launch_status();
 }

@@ -100,7 +100,7 @@ __global__ void latent_q_rotate_kernel(const float* __restrict__ q, const float*
 // A block takes ROWS rows of one head; a warp takes output channels in turn, its lanes the input channels, so a
 // weight row is read once per ROWS rows; sums run lane-wise in index order and then over a fixed butterfly.
 constexpr int PH_ROWS = 8;
-constexpr int PH_OUTS = 32;       // output channels of a block
+constexpr int PH_OUTS = 16;       // output channels of a block
 template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(128)
 per_head_linear_kernel(const TA* __restrict__ a, long long lda, int a_head, const TW* __restrict__ w, TO* __restrict__ out,
@@ -129,8 +129,9 @@ per_head_linear_kernel(const TA* __restrict__ a, long long lda, int a_head, cons
         }
 #pragma unroll
         for (int r = 0; r < PH_ROWS; r++) {
+            if (r >= rows) break;                   // the same for every lane
             const float s = warp_sum(acc[r]);
-            if (lane == 0 && r < rows) out[(size_t)(n0 + r) * ldo + (size_t)h * o_head + j] = from_f32<TO>(s);
+            if (lane == 0) out[(size_t)(n0 + r) * ldo + (size_t)h * o_head + j] = from_f32<TO>(s);
         }
     }
 }
@@ -216,7 +217,7 @@ int launch_per_head_mma(const void* a, int a_dtype, long long lda, int a_head, c
                         long long ldo, int o_head, int n_rows, int H, int kin, int nout, cudaStream_t stream) {
     dim3 grid((n_rows + PHM_T - 1) / PHM_T, H, (nout + PHM_T - 1) / PHM_T);
 #define ESP_PHM(TA, TO)                                                                                                     \
-    esp_launch_pdl(ESP_PDL_SMALL, per_head_mma_kernel<TA, TO>, grid, dim3(128), 0, stream, (const TA*)a, lda, a_head,         \
+    esp_launch_pdl(0, per_head_mma_kernel<TA, TO>, grid, dim3(128), 0, stream, (const TA*)a, lda, a_head,                     \
                    (const bf16*)w, (TO*)out, ldo, o_head, n_rows, kin, nout)
     switch (a_dtype * 2 + o_dtype) {
         case 0: ESP_PHM(float, float); break;

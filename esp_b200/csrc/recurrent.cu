@@ -61,6 +61,7 @@ __global__ void token_shift_keep_kernel(const T* __restrict__ h, float* __restri
 // ---------------------------------------------------------------------------------------------- the recurrence
 constexpr int SCAN_THREADS = 128;
 constexpr int KT = 16;          // key channels a thread keeps
+constexpr int KTP = KT + 4;     // a slice's stride in shared memory: slices 80 bytes apart fall into different banks
 constexpr int CHUNK = 16;       // tokens staged at a time
 constexpr int MAX_K = 8 * KT;   // key channels of a head that the kernel takes
 
@@ -99,7 +100,8 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
                   const int* __restrict__ seq_slot, float* __restrict__ out, int H, int K, int V, int ks, int vt) {
     pdl_trigger();
     extern __shared__ __align__(16) float smem[];
-    const int kp = ks * KT;                        // key channels, padded to the threads' slices
+    const int kp = ks * KTP;                       // floats of one token's q (or k, or d): the threads' slices, padded
+    auto at = [](int c) { return (c / KT) * KTP + (c % KT); };     // where key channel c lies in such a row
     // per buffer: q[CHUNK][kp], k[CHUNK][kp], d[CHUNK][kp], v[CHUNK][vt]
     const int buf_floats = CHUNK * (3 * kp + vt);
     const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * vt;
@@ -113,7 +115,7 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
 
     // constants of the head: bias / lower bound / bonus per key channel
     __shared__ float c_bias[MAX_K], c_lower[MAX_K], c_bonus[MAX_K];
-    for (int i = tid; i < kp; i += SCAN_THREADS) {
+    for (int i = tid; i < ks * KT; i += SCAN_THREADS) {
         const bool in = i < K;
         c_bias[i] = in && gate_bias ? gate_bias[h * K + i] : 0.f;
         c_lower[i] = in && lower ? lower[h * K + i] : 0.f;
@@ -143,9 +145,9 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
             for (int i = tid; i < count * k4; i += SCAN_THREADS) {
                 const int t = i / k4, c = (i - t * k4) * 4;
                 const size_t r = (size_t)(r0 + t);
-                cp_async16(base + t * kp + c, q + r * ldq + h * K + c);
-                if (MODE == GATE_EXP_EXP || READY) cp_async16(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
-                cp_async16(base + (2 * CHUNK + t) * kp + c, g + r * ldg + h * K + c);
+                cp_async16(base + t * kp + at(c), q + r * ldq + h * K + c);
+                if (MODE == GATE_EXP_EXP || READY) cp_async16(base + (CHUNK + t) * kp + at(c), k + r * ldk + h * K + c);
+                cp_async16(base + (2 * CHUNK + t) * kp + at(c), g + r * ldg + h * K + c);
             }
             for (int i = tid; i < count * v4; i += SCAN_THREADS) {
                 const int t = i / v4, c = (i - t * v4) * 4;
@@ -155,9 +157,9 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
             for (int i = tid; i < count * K; i += SCAN_THREADS) {
                 const int t = i / K, c = i - t * K;
                 const size_t r = (size_t)(r0 + t);
-                cp_async4(base + t * kp + c, q + r * ldq + h * K + c);
-                if (MODE == GATE_EXP_EXP || READY) cp_async4(base + (CHUNK + t) * kp + c, k + r * ldk + h * K + c);
-                cp_async4(base + (2 * CHUNK + t) * kp + c, g + r * ldg + h * K + c);
+                cp_async4(base + t * kp + at(c), q + r * ldq + h * K + c);
+                if (MODE == GATE_EXP_EXP || READY) cp_async4(base + (CHUNK + t) * kp + at(c), k + r * ldk + h * K + c);
+                cp_async4(base + (2 * CHUNK + t) * kp + at(c), g + r * ldg + h * K + c);
             }
             for (int i = tid; i < count * vt; i += SCAN_THREADS) {
                 const int t = i / vt, c = i - t * vt;
@@ -179,24 +181,24 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
         if (!READY) {
             // gates, in place
             for (int i = tid; i < count * K; i += SCAN_THREADS) {
-                const int t = i / K, c = i - t * K;
-                const float raw = __fadd_rn(sd[t * kp + c], c_bias[c]);
+                const int t = i / K, c = i - t * K, p = t * kp + at(c);
+                const float raw = __fadd_rn(sd[p], c_bias[c]);
                 if (MODE == GATE_EXP_EXP) {
-                    sd[t * kp + c] = gate_decay(raw);
+                    sd[p] = gate_decay(raw);
                 } else {
                     const float d = gate_lower(raw, c_lower[c]);
-                    sd[t * kp + c] = d;
-                    sk[t * kp + c] = __fsub_rn(1.0f, d);
-                    sq[t * kp + c] = gate_silu(sq[t * kp + c]);
+                    sd[p] = d;
+                    sk[p] = __fsub_rn(1.0f, d);
+                    sq[p] = gate_silu(sq[p]);
                 }
             }
             __syncthreads();
         }
 #pragma unroll 4
         for (int t = 0; t < count; t++) {
-            const float4* tq = reinterpret_cast<const float4*>(sq + t * kp + part * KT);
-            const float4* tk = reinterpret_cast<const float4*>(sk + t * kp + part * KT);
-            const float4* td = reinterpret_cast<const float4*>(sd + t * kp + part * KT);
+            const float4* tq = reinterpret_cast<const float4*>(sq + t * kp + part * KTP);
+            const float4* tk = reinterpret_cast<const float4*>(sk + t * kp + part * KTP);
+            const float4* td = reinterpret_cast<const float4*>(sd + t * kp + part * KTP);
             const float vv = live ? sv[t * vt + col] : 0.f;
             float oe[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -339,7 +341,7 @@ ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, c
     if (ks > 8) return (int)cudaErrorInvalidValue;
     const int vt = SCAN_THREADS / ks;              // value columns of a block
     const int vtiles = (V + vt - 1) / vt;
-    const size_t smem = 2 * (size_t)CHUNK * (3 * ks * KT + vt) * sizeof(float);
+    const size_t smem = 2 * (size_t)CHUNK * (3 * ks * KTP + vt) * sizeof(float);
     dim3 grid(n_seqs, H, vtiles);
     if ((mode == GATE_EXP_EXP || ready) && !k) return (int)cudaErrorInvalidValue;
 #define ESP_SCAN(MODE_, READY_)                                                                                              \
@@ -347,7 +349,8 @@ ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, c
         auto kernel = gated_scan_kernel<MODE_, READY_>;                                                                     \
         static bool set = false;                                                                                            \
         if (!set) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set = true; }      \
-        esp_launch_pdl(ESP_PDL_SMALL, kernel, grid, dim3(SCAN_THREADS), smem, stream, q, ldq, k, ldk, g, ldg, v, ldv,         \
+        /* a step of many rows runs long and holds its shared memory: no early start beside its predecessor */             \
+        esp_launch_pdl(READY_ ? 0 : ESP_PDL_SMALL, kernel, grid, dim3(SCAN_THREADS), smem, stream, q, ldq, k, ldk, g, ldg, v, ldv, \
                        gate_bias, lower, bonus, state, state_stride, seq_start, seq_slot, out, H, K, V, ks, vt);            \
     }
     if (mode == GATE_EXP_EXP && !ready) ESP_SCAN(GATE_EXP_EXP, false)
