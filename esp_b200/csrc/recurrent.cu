@@ -59,7 +59,8 @@ __global__ void token_shift_keep_kernel(const T* __restrict__ h, float* __restri
 }
 
 // ---------------------------------------------------------------------------------------------- the recurrence
-constexpr int SCAN_THREADS = 128;
+constexpr int SCAN_THREADS = 128;   // at most; a step with few blocks takes 64, so that an SM's shared-memory pipe serves fewer warps
+constexpr int CPT = 2;              // value columns a thread keeps: a token's q, k, d are read once for both
 constexpr int KT = 16;          // key channels a thread keeps
 constexpr int KTP = KT + 4;     // a slice's stride in shared memory: slices 80 bytes apart fall into different banks
 constexpr int CHUNK = 16;       // tokens staged at a time
@@ -105,30 +106,34 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
     // per buffer: q[CHUNK][kp], k[CHUNK][kp], d[CHUNK][kp], v[CHUNK][vt]
     const int buf_floats = CHUNK * (3 * kp + vt);
     const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * vt;
-    const int tid = threadIdx.x;
-    const int part = tid % ks, col = tid / ks;     // neighbouring lanes hold the slices of one column
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    const int part = tid % ks, col = (tid / ks) * CPT;   // neighbouring lanes hold the slices of one pair of columns
     const int vcol = v0 + col;
-    const bool live = col < vt && vcol < V;
+    bool live[CPT];
+#pragma unroll
+    for (int j = 0; j < CPT; j++) live[j] = col + j < vt && vcol + j < V;
     const int row0 = seq_start[b], row1 = seq_start[b + 1];
     if (row1 <= row0) return;
-    float* srow = state + (size_t)seq_slot[b] * state_stride + ((size_t)h * V + (live ? vcol : 0)) * K + part * KT;
+    float* srow = state + (size_t)seq_slot[b] * state_stride + ((size_t)h * V + vcol) * K + part * KT;   // column j: + j * K
 
     // constants of the head: bias / lower bound / bonus per key channel
     __shared__ float c_bias[MAX_K], c_lower[MAX_K], c_bonus[MAX_K];
-    for (int i = tid; i < ks * KT; i += SCAN_THREADS) {
+    for (int i = tid; i < ks * KT; i += nthreads) {
         const bool in = i < K;
         c_bias[i] = in && gate_bias ? gate_bias[h * K + i] : 0.f;
         c_lower[i] = in && lower ? lower[h * K + i] : 0.f;
         c_bonus[i] = in && bonus ? bonus[h * K + i] : 1.f;
     }
     // zero the padding of both buffers once (cp.async never writes it)
-    for (int i = tid; i < 2 * buf_floats; i += SCAN_THREADS) smem[i] = 0.f;
+    for (int i = tid; i < 2 * buf_floats; i += nthreads) smem[i] = 0.f;
     __syncthreads();
 
     pdl_wait();
-    float S[KT];
+    float S[CPT][KT];
 #pragma unroll
-    for (int i = 0; i < KT; i++) S[i] = (live && part * KT + i < K) ? srow[i] : 0.f;
+    for (int j = 0; j < CPT; j++)
+#pragma unroll
+        for (int i = 0; i < KT; i++) S[j][i] = (live[j] && part * KT + i < K) ? srow[(size_t)j * K + i] : 0.f;
 
     // 16-byte copies where every row piece is aligned (the usual case: K, V and the row strides multiples of 4)
     const bool wide = (K % 4 == 0) && (V % 4 == 0) && (vt % 4 == 0) && (ldq % 4 == 0) && (ldg % 4 == 0) && (ldv % 4 == 0) &&
@@ -142,26 +147,26 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
         const int count = min(CHUNK, row1 - r0);
         if (wide) {
             const int k4 = K / 4, v4 = vt / 4;
-            for (int i = tid; i < count * k4; i += SCAN_THREADS) {
+            for (int i = tid; i < count * k4; i += nthreads) {
                 const int t = i / k4, c = (i - t * k4) * 4;
                 const size_t r = (size_t)(r0 + t);
                 cp_async16(base + t * kp + at(c), q + r * ldq + h * K + c);
                 if (MODE == GATE_EXP_EXP || READY) cp_async16(base + (CHUNK + t) * kp + at(c), k + r * ldk + h * K + c);
                 cp_async16(base + (2 * CHUNK + t) * kp + at(c), g + r * ldg + h * K + c);
             }
-            for (int i = tid; i < count * v4; i += SCAN_THREADS) {
+            for (int i = tid; i < count * v4; i += nthreads) {
                 const int t = i / v4, c = (i - t * v4) * 4;
                 if (v0 + c < V) cp_async16(base + 3 * CHUNK * kp + t * vt + c, v + (size_t)(r0 + t) * ldv + h * V + v0 + c);
             }
         } else {
-            for (int i = tid; i < count * K; i += SCAN_THREADS) {
+            for (int i = tid; i < count * K; i += nthreads) {
                 const int t = i / K, c = i - t * K;
                 const size_t r = (size_t)(r0 + t);
                 cp_async4(base + t * kp + at(c), q + r * ldq + h * K + c);
                 if (MODE == GATE_EXP_EXP || READY) cp_async4(base + (CHUNK + t) * kp + at(c), k + r * ldk + h * K + c);
                 cp_async4(base + (2 * CHUNK + t) * kp + at(c), g + r * ldg + h * K + c);
             }
-            for (int i = tid; i < count * vt; i += SCAN_THREADS) {
+            for (int i = tid; i < count * vt; i += nthreads) {
                 const int t = i / vt, c = i - t * vt;
                 if (v0 + c < V) cp_async4(base + 3 * CHUNK * kp + t * vt + c, v + (size_t)(r0 + t) * ldv + h * V + v0 + c);
             }
@@ -180,7 +185,7 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
         float* sq = base, *sk = base + CHUNK * kp, *sd = base + 2 * CHUNK * kp, *sv = base + 3 * CHUNK * kp;
         if (!READY) {
             // gates, in place
-            for (int i = tid; i < count * K; i += SCAN_THREADS) {
+            for (int i = tid; i < count * K; i += nthreads) {
                 const int t = i / K, c = i - t * K, p = t * kp + at(c);
                 const float raw = __fadd_rn(sd[p], c_bias[c]);
                 if (MODE == GATE_EXP_EXP) {
@@ -194,13 +199,17 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
             }
             __syncthreads();
         }
-#pragma unroll 4
+#pragma unroll 2
         for (int t = 0; t < count; t++) {
             const float4* tq = reinterpret_cast<const float4*>(sq + t * kp + part * KTP);
             const float4* tk = reinterpret_cast<const float4*>(sk + t * kp + part * KTP);
             const float4* td = reinterpret_cast<const float4*>(sd + t * kp + part * KTP);
-            const float vv = live ? sv[t * vt + col] : 0.f;
-            float oe[4] = {0.f, 0.f, 0.f, 0.f};
+            float vv[CPT], oe[CPT][4];
+#pragma unroll
+            for (int j = 0; j < CPT; j++) {
+                vv[j] = live[j] ? sv[t * vt + col + j] : 0.f;
+                oe[j][0] = oe[j][1] = oe[j][2] = oe[j][3] = 0.f;
+            }
 #pragma unroll
             for (int i4 = 0; i4 < KT / 4; i4++) {
                 const float4 q4 = tq[i4], k4 = tk[i4], d4 = td[i4];
@@ -208,25 +217,33 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
                     const int i = 4 * i4 + e;
-                    const float a = ke[e] * vv;
-                    if (MODE == GATE_EXP_EXP) {
-                        oe[e] = fmaf(qe[e], fmaf(bonus_r[i], a, S[i]), oe[e]);
-                        S[i] = fmaf(de[e], S[i], a);
-                    } else {
-                        S[i] = fmaf(de[e], S[i], a);
-                        oe[e] = fmaf(qe[e], S[i], oe[e]);
+#pragma unroll
+                    for (int j = 0; j < CPT; j++) {
+                        const float a = ke[e] * vv[j];
+                        if (MODE == GATE_EXP_EXP) {
+                            oe[j][e] = fmaf(qe[e], fmaf(bonus_r[i], a, S[j][i]), oe[j][e]);
+                            S[j][i] = fmaf(de[e], S[j][i], a);
+                        } else {
+                            S[j][i] = fmaf(de[e], S[j][i], a);
+                            oe[j][e] = fmaf(qe[e], S[j][i], oe[j][e]);
+                        }
                     }
                 }
             }
-            float o = (oe[0] + oe[1]) + (oe[2] + oe[3]);
-            for (int off = 1; off < ks; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-            if (live && part == 0) out[(size_t)(r0 + t) * H * V + h * V + vcol] = o;
+#pragma unroll
+            for (int j = 0; j < CPT; j++) {
+                float o = (oe[j][0] + oe[j][1]) + (oe[j][2] + oe[j][3]);
+                for (int off = 1; off < ks; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+                if (live[j] && part == 0) out[(size_t)(r0 + t) * H * V + h * V + vcol + j] = o;
+            }
         }
     }
-    if (live) {
+#pragma unroll
+    for (int j = 0; j < CPT; j++) {
+        if (!live[j]) continue;
 #pragma unroll
         for (int i = 0; i < KT; i++)
-            if (part * KT + i < K) srow[i] = S[i];
+            if (part * KT + i < K) srow[(size_t)j * K + i] = S[j][i];
     }
 }
 
@@ -339,7 +356,11 @@ ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, c
     int ks = 1;
     while (ks * KT < K) ks <<= 1;                  // 1, 2, 4 or 8 slices of KT channels
     if (ks > 8) return (int)cudaErrorInvalidValue;
-    const int vt = SCAN_THREADS / ks;              // value columns of a block
+    // value columns of a block; with few blocks in all, blocks of half the size: the tokens are a chain, and what
+    // bounds a block's pace is the shared-memory traffic of the warps that share its SM
+    int threads = SCAN_THREADS;
+    if ((long long)n_seqs * H * ((V + (threads / ks) * CPT - 1) / ((threads / ks) * CPT)) < 148 && ks <= 32 && V > (64 / ks) * CPT) threads = 64;
+    const int vt = (threads / ks) * CPT;
     const int vtiles = (V + vt - 1) / vt;
     const size_t smem = 2 * (size_t)CHUNK * (3 * ks * KTP + vt) * sizeof(float);
     dim3 grid(n_seqs, H, vtiles);
@@ -350,7 +371,7 @@ ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, c
         static bool set = false;                                                                                            \
         if (!set) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set = true; }      \
         /* a step of many rows runs long and holds its shared memory: no early start beside its predecessor */             \
-        esp_launch_pdl(READY_ ? 0 : ESP_PDL_SMALL, kernel, grid, dim3(SCAN_THREADS), smem, stream, q, ldq, k, ldk, g, ldg, v, ldv, \
+        esp_launch_pdl(READY_ ? 0 : ESP_PDL_SMALL, kernel, grid, dim3(threads), smem, stream, q, ldq, k, ldk, g, ldg, v, ldv, \
                        gate_bias, lower, bonus, state, state_stride, seq_start, seq_slot, out, H, K, V, ks, vt);            \
     }
     if (mode == GATE_EXP_EXP && !ready) ESP_SCAN(GATE_EXP_EXP, false)
