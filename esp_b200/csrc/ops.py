@@ -697,7 +697,7 @@ def token_shift_keep(h, prev_state, seq_start, seq_slot, n_seqs: int):
 
 SCAN_DECAY_BONUS = 0          # d = exp(-exp(g + bias)), the current token weighted by ``bonus``, output before the update
 SCAN_LOWER_SIGMOID = 1        # d = lower + (1 - lower) sigmoid(g + bias), k = 1 - d, q = silu(q), output after the update
-SCAN_MAX_KEY_DIM = 128
+SCAN_MAX_KEY_DIM = 256
 
 
 def gate_prepare(mode, q, g, gate_bias, lower, q_out, k_out, d_out):

@@ -59,12 +59,25 @@ __global__ void token_shift_keep_kernel(const T* __restrict__ h, float* __restri
 }
 
 // ---------------------------------------------------------------------------------------------- the recurrence
-constexpr int SCAN_THREADS = 128;   // at most; a step with few blocks takes 64, so that an SM's shared-memory pipe serves fewer warps
-constexpr int CPT = 2;              // value columns a thread keeps: a token's q, k, d are read once for both
+constexpr int SCAN_THREADS = 128;
+// Tiling constants that were measured against each other (2,048 tokens of one sequence, 16 heads of 128 x 128, and
+// eight such sequences): columns per thread 1 / 2 / 4: 588 / 793 / 1,258 us and 2,464 / 1,862 / 1,540 us; blocks of 64
+// threads for short grids: 627 us; no unrolling of the token loop: 625 us.  The defaults serve the single long prompt.
+#ifndef ESP_SCAN_CPT
+#define ESP_SCAN_CPT 1
+#endif
+#ifndef ESP_SCAN_SMALL_THREADS
+#define ESP_SCAN_SMALL_THREADS 128
+#endif
+#ifndef ESP_SCAN_UNROLL
+#define ESP_SCAN_UNROLL 4
+#endif
+constexpr int SCAN_UNROLL = ESP_SCAN_UNROLL;
+constexpr int CPT = ESP_SCAN_CPT;   // value columns a thread keeps: a token's q, k, d are read once for all of them
 constexpr int KT = 16;          // key channels a thread keeps
 constexpr int KTP = KT + 4;     // a slice's stride in shared memory: slices 80 bytes apart fall into different banks
 constexpr int CHUNK = 16;       // tokens staged at a time
-constexpr int MAX_K = 8 * KT;   // key channels of a head that the kernel takes
+constexpr int MAX_K = 16 * KT;  // key channels of a head that the kernel takes
 
 enum : int {
     GATE_EXP_EXP = 0,      // d = exp(-exp(g + bias));  k, q as given;  o reads S_(t-1) + diag(bonus) k v^T
@@ -199,7 +212,7 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
             }
             __syncthreads();
         }
-#pragma unroll 2
+#pragma unroll SCAN_UNROLL
         for (int t = 0; t < count; t++) {
             const float4* tq = reinterpret_cast<const float4*>(sq + t * kp + part * KTP);
             const float4* tk = reinterpret_cast<const float4*>(sk + t * kp + part * KTP);
@@ -354,12 +367,11 @@ ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, c
     if (n_seqs <= 0) return 0;
     if (K <= 0 || V <= 0 || K > MAX_K || H > 65535) return (int)cudaErrorInvalidValue;
     int ks = 1;
-    while (ks * KT < K) ks <<= 1;                  // 1, 2, 4 or 8 slices of KT channels
-    if (ks > 8) return (int)cudaErrorInvalidValue;
-    // value columns of a block; with few blocks in all, blocks of half the size: the tokens are a chain, and what
-    // bounds a block's pace is the shared-memory traffic of the warps that share its SM
+    while (ks * KT < K) ks <<= 1;                  // 1, 2, 4, 8 or 16 slices of KT channels
+    if (ks > 16) return (int)cudaErrorInvalidValue;
+    // value columns of a block (ESP_SCAN_SMALL_THREADS < 128: smaller blocks for grids that leave SMs empty)
     int threads = SCAN_THREADS;
-    if ((long long)n_seqs * H * ((V + (threads / ks) * CPT - 1) / ((threads / ks) * CPT)) < 148 && ks <= 32 && V > (64 / ks) * CPT) threads = 64;
+    if ((long long)n_seqs * H * ((V + (threads / ks) * CPT - 1) / ((threads / ks) * CPT)) < 148 && ks <= 32 && V > (64 / ks) * CPT) threads = ESP_SCAN_SMALL_THREADS;
     const int vt = (threads / ks) * CPT;
     const int vtiles = (V + vt - 1) / vt;
     const size_t smem = 2 * (size_t)CHUNK * (3 * ks * KTP + vt) * sizeof(float);
@@ -369,7 +381,7 @@ ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, c
     {                                                                                                                       \
         auto kernel = gated_scan_kernel<MODE_, READY_>;                                                                     \
         static bool set = false;                                                                                            \
-        if (!set) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); set = true; }      \
+        if (!set) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024); set = true; }     \
         /* a step of many rows runs long and holds its shared memory: no early start beside its predecessor */             \
         esp_launch_pdl(READY_ ? 0 : ESP_PDL_SMALL, kernel, grid, dim3(threads), smem, stream, q, ldq, k, ldk, g, ldg, v, ldv, \
                        gate_bias, lower, bonus, state, state_stride, seq_start, seq_slot, out, H, K, V, ks, vt);            \

@@ -41,7 +41,7 @@ def scan_reference(mode, q, k, g, v, bias, lower, bonus, S):
 
 
 @pytest.mark.parametrize("mode", [ops.SCAN_DECAY_BONUS, ops.SCAN_LOWER_SIGMOID])
-@pytest.mark.parametrize("H,K,V", [(3, 24, 40), (1, 128, 72), (2, 16, 16), (5, 64, 130), (2, 100, 8)])
+@pytest.mark.parametrize("H,K,V", [(3, 24, 40), (1, 128, 72), (2, 16, 16), (5, 64, 130), (2, 100, 8), (1, 200, 24), (2, 256, 7)])
 def test_gated_scan_runs_cuts_and_slots(mode, H, K, V):
     torch.manual_seed(H * 1000 + K + V + mode)
     runs = [37, 1, 20]                       # three sequences of unequal length in one call
