@@ -277,34 +277,35 @@ attn_latent_mma_kernel(const bf16* __restrict__ qx, const bf16* __restrict__ poo
 }
 
 // out[n, h] = sum_s w_s O_s / sum_s w_s l_s with w_s = exp(m_s - max m), splits added in ascending order.  A warp a row.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 attn_latent_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out, int rows,
                            int n_splits, int hdv) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float wts[];                  // [warps of the block][n_splits]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (row >= rows) return;
-    float* w = wts + warp * n_splits;
+    extern __shared__ float wts[];                  // [n_splits] weights of the splits, then their sum
+    const int row = blockIdx.x, tid = threadIdx.x;
     const float* ml = part_ml + (size_t)row * n_splits * 2;
-    float m = -INFINITY;
-    for (int s = lane; s < n_splits; s += 32) m = fmaxf(m, ml[2 * s]);
-    m = warp_max(m);
-    for (int s = lane; s < n_splits; s += 32) w[s] = ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - m);
-    __syncwarp();
-    float l = 0.f;
-    for (int s = 0; s < n_splits; s++) l = fmaf(w[s], ml[2 * s + 1], l);
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    if (tid < 32) {
+        float m = -INFINITY;
+        for (int s = tid; s < n_splits; s += 32) m = fmaxf(m, ml[2 * s]);
+        m = warp_max(m);
+        for (int s = tid; s < n_splits; s += 32) wts[s] = ml[2 * s] == -INFINITY ? 0.f : expf(ml[2 * s] - m);
+        __syncwarp();
+        if (tid == 0) {
+            float l = 0.f;
+            for (int s = 0; s < n_splits; s++) l = fmaf(wts[s], ml[2 * s + 1], l);
+            wts[n_splits] = l > 0.f ? 1.0f / l : 0.f;
+        }
+    }
+    __syncthreads();
+    const float inv = wts[n_splits];
     const float* po = part_o + (size_t)row * n_splits * hdv;
-    for (int c0 = 0; c0 < hdv; c0 += 128) {         // four channels a lane, every split's piece one 16-byte load
-        const int c = c0 + lane * 4;
-        if (c >= hdv) continue;
+    for (int c = tid * 4; c < hdv; c += blockDim.x * 4) {     // four channels a thread, every split's piece one 16-byte load
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
+#pragma unroll 8
         for (int s = 0; s < n_splits; s++) {
             const float4 v = *reinterpret_cast<const float4*>(po + (size_t)s * hdv + c);
-            const float ws = w[s];
+            const float ws = wts[s];
             acc.x = fmaf(ws, v.x, acc.x);
             acc.y = fmaf(ws, v.y, acc.y);
             acc.z = fmaf(ws, v.z, acc.z);
@@ -360,9 +361,10 @@ ESP_API int esp_attn_latent_mma(const void* qx, const void* pool, void* out, con
 #undef ESP_GO
     if (code != 0 || n_splits == 1) return code;
     const long long rows = (long long)n_rows * H;
-    if ((size_t)8 * n_splits * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
-    esp_launch_pdl(ESP_PDL_ATTENTION, attn_latent_combine_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256),
-                   (size_t)8 * n_splits * sizeof(float), stream,
+    if ((size_t)(n_splits + 1) * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+    const int threads = hdv / 4 >= 128 ? 128 : (hdv / 4 + 31) / 32 * 32;
+    esp_launch_pdl(ESP_PDL_ATTENTION, attn_latent_combine_kernel, dim3((unsigned)rows), dim3(threads),
+                   (size_t)(n_splits + 1) * sizeof(float), stream,
                    (const float*)part_o, (const float*)part_ml, (bf16*)out, (int)rows, n_splits, hdv);
     return esp_launch_status();
 }

@@ -354,11 +354,17 @@ __global__ void xielu_kernel(const float* __restrict__ z, const float* __restric
     pdl_trigger();
     pdl_wait();
     const float ap = softplus_f(pq[0]), an = 0.5f + softplus_f(pq[1]);
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
-        const float v = z[i];
-        const float r = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
-        act[i] = from_f32<TO>(r);
+    auto f = [&](float v) { return v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v); };
+    if (count % 4 == 0 && ((size_t)z % 16) == 0 && ((size_t)act % 16) == 0) {       // four values a piece
+        const long long pieces = count / 4;
+        for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < pieces; i += (long long)gridDim.x * blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(z)[i];
+            Vec4<TO>::store(act + 4 * i, f(v.x), f(v.y), f(v.z), f(v.w));
+        }
+        return;
     }
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x)
+        act[i] = from_f32<TO>(f(z[i]));
 }
 
 ESP_API int esp_xielu(const float* z, const float* pq, void* act, int act_is_bf16, long long count, cudaStream_t stream) {

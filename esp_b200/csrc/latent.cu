@@ -154,6 +154,15 @@ __device__ __forceinline__ void phm_mma(float (&c)[4], const unsigned (&a)[4], u
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ uint4 load8(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ uint4 load8(const float* p) {
+    const float4 lo = *reinterpret_cast<const float4*>(p), hi = *reinterpret_cast<const float4*>(p + 4);
+    __nv_bfloat162 a = __floats2bfloat162_rn(lo.x, lo.y), b = __floats2bfloat162_rn(lo.z, lo.w);
+    __nv_bfloat162 c = __floats2bfloat162_rn(hi.x, hi.y), d = __floats2bfloat162_rn(hi.z, hi.w);
+    return make_uint4(*reinterpret_cast<unsigned*>(&a), *reinterpret_cast<unsigned*>(&b), *reinterpret_cast<unsigned*>(&c),
+                      *reinterpret_cast<unsigned*>(&d));
+}
+
 template <typename TA, typename TO>
 __global__ void __launch_bounds__(128)
 per_head_mma_kernel(const TA* __restrict__ a, long long lda, int a_head, const bf16* __restrict__ w, TO* __restrict__ out,
@@ -166,6 +175,8 @@ per_head_mma_kernel(const TA* __restrict__ a, long long lda, int a_head, const b
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
     const int wr = (warp & 1) * 32, wc = (warp >> 1) * 32;
     const bf16* wh = w + (size_t)h * nout * kin;
+    // every piece of eight channels starts on a 16-byte boundary (32 for float inputs)
+    const bool wide = kin % 8 == 0 && lda % 8 == 0 && a_head % 8 == 0 && ((size_t)a % 32) == 0 && ((size_t)w % 16) == 0;
     float acc[2][4][4];
 #pragma unroll
     for (int i = 0; i < 2; i++)
@@ -175,13 +186,26 @@ per_head_mma_kernel(const TA* __restrict__ a, long long lda, int a_head, const b
             for (int k = 0; k < 4; k++) acc[i][j][k] = 0.f;
     for (int k0 = 0; k0 < kin; k0 += PHM_KC) {
         __syncthreads();
-        for (int idx = tid; idx < PHM_T * PHM_KC; idx += 128) {
-            const int r = idx / PHM_KC, c = idx - r * PHM_KC;
-            const int k = k0 + c;
-            const bool kin_ok = k < kin;
-            as[r * PHM_LD + c] = (kin_ok && n0 + r < n_rows)
-                ? __float2bfloat16_rn(to_f32(a[(size_t)(n0 + r) * lda + (size_t)h * a_head + k])) : __float2bfloat16_rn(0.f);
-            ws[r * PHM_LD + c] = (kin_ok && j0 + r < nout) ? wh[(size_t)(j0 + r) * kin + k] : __float2bfloat16_rn(0.f);
+        if (wide) {
+            // eight channels a piece: 16 bytes of bfloat16, or two float4 rounded to bfloat16 on the way
+            for (int idx = tid; idx < PHM_T * (PHM_KC / 8); idx += 128) {
+                const int r = idx / (PHM_KC / 8), c = (idx - r * (PHM_KC / 8)) * 8;
+                const int k = k0 + c;
+                uint4 av = make_uint4(0u, 0u, 0u, 0u), wv = make_uint4(0u, 0u, 0u, 0u);
+                if (k < kin && n0 + r < n_rows) av = load8(a + (size_t)(n0 + r) * lda + (size_t)h * a_head + k);
+                if (k < kin && j0 + r < nout) wv = *reinterpret_cast<const uint4*>(wh + (size_t)(j0 + r) * kin + k);
+                *reinterpret_cast<uint4*>(as + r * PHM_LD + c) = av;
+                *reinterpret_cast<uint4*>(ws + r * PHM_LD + c) = wv;
+            }
+        } else {
+            for (int idx = tid; idx < PHM_T * PHM_KC; idx += 128) {
+                const int r = idx / PHM_KC, c = idx - r * PHM_KC;
+                const int k = k0 + c;
+                const bool kin_ok = k < kin;
+                as[r * PHM_LD + c] = (kin_ok && n0 + r < n_rows)
+                    ? __float2bfloat16_rn(to_f32(a[(size_t)(n0 + r) * lda + (size_t)h * a_head + k])) : __float2bfloat16_rn(0.f);
+                ws[r * PHM_LD + c] = (kin_ok && j0 + r < nout) ? wh[(size_t)(j0 + r) * kin + k] : __float2bfloat16_rn(0.f);
+            }
         }
         __syncthreads();
 #pragma unroll

@@ -112,13 +112,14 @@ class LatentAttention(Part):
                             s.scale, rt.status)
             return
         tile_first = ctx.arrays[f"latent.tiles{tq}.first"]
-        # few blocks and many pages: deal every tile's pages to several blocks, so that the cache streams at full width
+        # few blocks and many pages: deal every tile's pages to several blocks (about one block an SM in all), so that
+        # the cache streams at full width; every split costs a partial result of float values, so no more than that
         n = qx.shape[0]
         blocks = tile_seq.shape[0] * ((H + hg - 1) // hg)
         positions = table.shape[1] * layer.page
         span = min(positions, s.window + tq + layer.page) if s.window else positions
         pages = (span + layer.page - 1) // layer.page
-        n_splits = max(1, min(pages, (2 * rt.sm_count) // max(1, blocks)))
+        n_splits = max(1, min(pages, rt.sm_count // max(1, blocks)))
         part_o = part_ml = None
         per = 0
         if n_splits > 1:
