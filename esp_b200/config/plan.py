@@ -129,8 +129,8 @@ class LatentAttentionNames:
 
 @dataclass(frozen=True)
 class LatentAttentionSpec:
-    """Softmax attention whose keys and values are up-projections of one cached latent per position plus one
-    rotated key part shared by the heads.  Per head: ``nope_dim`` unrotated and ``rot_dim`` rotated query/key
+    """Softmax attention whose keys and values are up-projections of one cached latent per position; the keys have,
+    besides, one rotated part that is the same for every head.  Per head: ``nope_dim`` unrotated and ``rot_dim`` rotated query/key
     channels, ``value_dim`` value channels."""
     hidden: int
     num_heads: int
@@ -171,9 +171,9 @@ class GatedRecurrenceNames:
 
 @dataclass(frozen=True)
 class LowerBoundRecurrenceSpec:
-    """Linear attention whose forget gate f (bounded below per channel) also decides what is written:
-    S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T silu(q_t); per-head RMS norm with one weight vector
-    shared by the heads."""
+    """Gated linear recurrence with one gate for forgetting and writing: what a state row keeps, f_t, and what it
+    takes of the new value, 1 - f_t, add up to one, and f_t has a floor per channel:
+    S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T silu(q_t); RMS norm per head, one weight vector for all heads."""
     hidden: int
     num_heads: int
     key_dim: int
@@ -186,8 +186,8 @@ class LowerBoundRecurrenceSpec:
 
 @dataclass(frozen=True)
 class DecayBonusRecurrenceSpec:
-    """Time mixing with token shift, a data-dependent decay per key channel from a low-rank projection, and a
-    bonus for the current token: o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t, S_t = diag(w_t) S_(t-1) + k_t v_t^T;
+    """Time mixing with token shift, a data-dependent decay per key channel from a low-rank projection, and an
+    extra weight u on the token being read: o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t, S_t = diag(w_t) S_(t-1) + k_t v_t^T;
     per-head unit RMS, a weight per channel and a SiLU gate."""
     hidden: int
     num_heads: int

@@ -1,5 +1,5 @@
 // Attention through a low-rank latent: what is cached per position is one row [latent (rank) | rotated key part
-// (rot)], shared by all heads.  With the keys' up-projection folded into the queries and the values' up-projection
+// (rot)], the same for every head.  With the keys' up-projection folded into the queries and the values' up-projection
 // applied after the weighted sum, every head attends to the cached rows themselves:
 //     score(h, j) = (q_lat[h] . latent_j + q_rot[h] . krot_j) * scale,   q_lat[h] = W_uk[h]^T q_nope[h]
 //     o_lat[h]    = sum_j softmax(score)(h, j) latent_j,                 out[h]   = W_uv[h] o_lat[h]

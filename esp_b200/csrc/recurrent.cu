@@ -36,6 +36,39 @@ __global__ void token_shift_mix_kernel(const T* __restrict__ h, const float* __r
     const float* ps = prev_state + (size_t)seq_slot[seq] * state_stride;
     const T* cur = h + (size_t)n * width;
     const T* before = h + (size_t)(n - 1) * width;
+    if (sizeof(T) == 2 && width % 8 == 0 && ((size_t)h % 16) == 0 && ((size_t)out % 16) == 0 && state_stride % 4 == 0 &&
+        ((size_t)prev_state % 16) == 0) {
+        // eight channels a thread: one 16-byte load of the row (and of the row before), one 16-byte store per mix
+        for (int d = threadIdx.x * 8; d < width; d += blockDim.x * 8) {
+            float c[8], p[8];
+            const uint4 cv = *reinterpret_cast<const uint4*>(cur + d);
+            const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&cv);
+#pragma unroll
+            for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(c2[i]); c[2 * i] = f.x; c[2 * i + 1] = f.y; }
+            if (first) {
+                const float4 a = *reinterpret_cast<const float4*>(ps + d), b = *reinterpret_cast<const float4*>(ps + d + 4);
+                p[0] = a.x; p[1] = a.y; p[2] = a.z; p[3] = a.w; p[4] = b.x; p[5] = b.y; p[6] = b.z; p[7] = b.w;
+            } else {
+                const uint4 pv = *reinterpret_cast<const uint4*>(before + d);
+                const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&pv);
+#pragma unroll
+                for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(p2[i]); p[2 * i] = f.x; p[2 * i + 1] = f.y; }
+            }
+            for (int m = 0; m < n_mix; m++) {
+                const float* mm = mu + (size_t)m * width + d;
+                uint4 o;
+                unsigned* o1 = reinterpret_cast<unsigned*>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(fmaf(p[2 * i] - c[2 * i], mm[2 * i], c[2 * i]),
+                                                             fmaf(p[2 * i + 1] - c[2 * i + 1], mm[2 * i + 1], c[2 * i + 1]));
+                    o1[i] = *reinterpret_cast<unsigned*>(&v);
+                }
+                *reinterpret_cast<uint4*>(out + ((size_t)m * n_rows + n) * width + d) = o;
+            }
+        }
+        return;
+    }
     for (int d = threadIdx.x; d < width; d += blockDim.x) {
         const float c = to_f32(cur[d]);
         const float p = first ? ps[d] : to_f32(before[d]);
@@ -299,6 +332,29 @@ __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const floa
     const int n = warp / H, h = warp - n * H;
     const float* src = o + ((size_t)n * H + h) * V;
     float ss = 0.f;
+    if (V <= 256) {
+        // the head's values stay in registers: all loads in flight at once, one pass over memory
+        float val[8], gz[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int i = lane + 32 * j;
+            val[j] = i < V ? src[i] : 0.f;
+            gz[j] = (gate && i < V) ? gate[(size_t)n * ldgate + h * V + i] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) ss = fmaf(val[j], val[j], ss);      // lane-wise in index order, as the loop below
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int i = lane + 32 * j;
+            if (i >= V) break;
+            float r = val[j] * inv * w[h * w_head_stride + i];
+            if (gate) r *= gz[j] / (1.0f + expf(-gz[j]));
+            y[((size_t)n * H + h) * V + i] = from_f32<T>(r);
+        }
+        return;
+    }
     for (int i = lane; i < V; i += 32) ss = fmaf(src[i], src[i], ss);
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)V + eps);
@@ -358,7 +414,7 @@ ESP_API int esp_gate_prepare(int mode, const float* q, long long ldq, const floa
     return esp_launch_status();
 }
 
-// mode: 0 = decay exp(-exp(.)) with a bonus for the current token, 1 = lower-bounded sigmoid gate that also writes.
+// mode: 0 = decay exp(-exp(.)) with an extra weight on the token being read, 1 = lower-bounded sigmoid gate that also writes.
 // ready: q, k and g already hold the query, the written key and the decay (esp_gate_prepare made them).
 ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, const float* k, long long ldk, const float* g,
                            long long ldg, const float* v, long long ldv, const float* gate_bias, const float* lower,

@@ -1,4 +1,4 @@
-"""Attention through a cached low-rank latent, with a sliding window and a rotated key part shared by the heads."""
+"""Attention through a cached low-rank latent, with a sliding window and one rotated key part for all heads."""
 from __future__ import annotations
 
 import numpy as np
@@ -16,7 +16,7 @@ class LatentAttention(Part):
     kv_rank rows, normed) and one rotated key part for all heads; per head the unrotated key is W_uk c and the value
     W_uv c; score = (q_nope . k_nope + q_rot . k_rot) * scale over the window; softmax; W_o on the heads.
 
-    Only c and the rotated key part are cached, one row [c | k_rot] per position.  The keys' up-projection is
+    The cache holds one row [c | k_rot] per position and nothing per head.  The keys' up-projection is
     folded into the query (q_lat = W_uk^T q_nope per head) and the values' up-projection is applied to the
     weighted sum of latents, so every head attends to the cached rows themselves.  A layer without a
     down-projection of its own (``own_kv`` False) reads the rows another layer cached, with its own window."""

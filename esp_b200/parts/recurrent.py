@@ -1,7 +1,7 @@
 """Mixers with a recurrent state of fixed size per sequence: two forms of the gated outer-product recurrence
-S_t = diag(d_t) S_(t-1) + k_t v_t^T per head.  The state lives in 32-bit floats in the cache's per-slot state
-rows, starts at zero when a slot is opened, and is carried from step to step; a step may bring any run of tokens
-of a sequence.  Both run on ``ops.gated_scan``, which makes the gates from the projections' raw outputs."""
+S_t = diag(d_t) S_(t-1) + k_t v_t^T per head.  A head's matrix S is float32 and belongs to the sequence: it sits in
+the cache's per-slot state rows, is zeroed when the slot is opened, and every step continues from what the step before
+left there, whatever run of tokens it brings.  Both run on ``ops.gated_scan``, which makes the gates from the projections' raw outputs."""
 from __future__ import annotations
 
 import torch
@@ -27,7 +27,7 @@ def _check_dims(kind, key_dim):
 class LowerBoundRecurrence(Part):
     """q = silu(W_q h), v = W_v h, f = lower + (1 - lower) sigmoid(W_f h + b_f) per head and key channel;
     S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T; o_t = S_t^T q_t; every head's o RMS-normed over its value channels
-    with one weight vector shared by the heads; then W_o.  The three projections are one packed product."""
+    with one weight vector for all heads; then W_o.  The three projections are one packed product."""
 
     graph_safe = True
 
@@ -98,7 +98,7 @@ class DecayBonusRecurrence(Part):
     """Each of r, k, v, g, w reads its own mix h + (h' - h) mu of a row and the row before it (h' is part of the
     state); r, k, v are projections of their mixes, gate = silu(W_g mix_g), the decay per head and key channel
     w = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0)); o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t, then
-    S_t = diag(w_t) S_(t-1) + k_t v_t^T; every head's o is divided by its root mean square, multiplied by a
+    S_t = diag(w_t) S_(t-1) + k_t v_t^T; every head's o is scaled to unit root mean square, multiplied by a
     weight per channel and by the gate; then W_o."""
 
     graph_safe = True

@@ -60,7 +60,7 @@ def hgrn2(h, w, pre, mix, eps):
 
 
 def wkv(h, w, pre, mix, eps):
-    """Token-shifted projections, a data-dependent decay per key channel, a bonus for the current token."""
+    """Token-shifted projections, a decay per key channel computed from the input, an extra weight u on the token being read."""
     H, K = mix["heads"], mix["dim"]
     T, D = h.shape
     prev = torch.cat([torch.zeros(1, D, dtype=h.dtype), h[:-1]], 0)
