@@ -36,6 +36,7 @@ struct SkinnyParams {
     const int* a_rows;
     const int* group_offsets;
     const float* row_scale;
+    const float* act_pq;            // plain form only: null, or the two raw numbers of an xIELU applied to every output
     void* C;
     long long ldc;
     int M, N, K;
@@ -56,6 +57,13 @@ struct SkinnyParams {
 };
 
 enum : int { MODE_PLAIN = 0, MODE_SWIGLU = 1, MODE_ROPE = 2 };
+
+// xIELU with a_p = softplus(p), a_n = 1/2 + softplus(q): a_p z^2 + z/2 for z > 0, a_n (exp(z) - 1 - z) + z/2 otherwise
+// (the same expressions as the stand-alone kernel in elementwise.cu)
+__device__ __forceinline__ float skinny_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float skinny_xielu(float v, float ap, float an) {
+    return v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
+}
 
 // One pair (x[i], x[i + hd/2]) of head ``head`` of token row m: bias, rotation in float with the same
 // operations in the same order as the separate kernel (rope_kv.cu), then the query row or the cache.
@@ -269,8 +277,14 @@ gemm_skinny_kernel(SkinnyParams p) {
                     } else {
                         const float scale = p.row_scale ? p.row_scale[m0 + tok] : 1.0f;
                         const int n_lo = tile * 16 + g, n_hi = n_lo + 8;
-                        if (n_lo < p.N) reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n_lo] = from_f32<TC>(acc[nb][i] * scale);
-                        if (n_hi < p.N) reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n_hi] = from_f32<TC>(acc[nb][2 + i] * scale);
+                        float v_lo = acc[nb][i] * scale, v_hi = acc[nb][2 + i] * scale;
+                        if (p.act_pq) {
+                            const float ap = skinny_softplus(p.act_pq[0]), an = 0.5f + skinny_softplus(p.act_pq[1]);
+                            v_lo = skinny_xielu(v_lo, ap, an);
+                            v_hi = skinny_xielu(v_hi, ap, an);
+                        }
+                        if (n_lo < p.N) reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n_lo] = from_f32<TC>(v_lo);
+                        if (n_hi < p.N) reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n_hi] = from_f32<TC>(v_hi);
                     }
                 }
             }
@@ -312,6 +326,7 @@ gemm_skinny_kernel(SkinnyParams p) {
                 const int n = (blockIdx.x * TILES + tl) * 16 + (ln >> 2) + (i >= 2 ? 8 : 0);
                 if (tok < cnt && n < p.N) {
                     if (p.row_scale) v *= p.row_scale[m0 + tok];
+                    if (p.act_pq) v = skinny_xielu(v, skinny_softplus(p.act_pq[0]), 0.5f + skinny_softplus(p.act_pq[1]));
                     reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n] = from_f32<TC>(v);
                 }
             }
@@ -374,13 +389,16 @@ int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
 
 // ``max_rows``: an upper bound of the rows of any one group (of M when dense); it
 // selects how many rows are staged at a time.  swiglu: N is the intermediate
-// size and W holds 2N rows per group.  c_dtype: 0 float, 1 bfloat16.
+// size and W holds 2N rows per group.  c_dtype: 0 float, 1 bfloat16.  act_pq (plain form): null, or two floats on the
+// device: every output passes through the xIELU they parameterise.
 ESP_API int esp_gemm_skinny(const void* A, long long lda, const int* a_rows, const void* W, long long w_group_stride,
                             const float* row_scale, void* C, int c_dtype, long long ldc, const int* group_offsets,
-                            int groups, int M, int N, int K, int max_rows, int swiglu, int offsets_ready, cudaStream_t stream) {
+                            int groups, int M, int N, int K, int max_rows, int swiglu, int offsets_ready, const float* act_pq,
+                            cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K % 8 != 0 || lda % 8 != 0 || groups > 65535) return (int)cudaErrorInvalidValue;
+    if (K % 8 != 0 || lda % 8 != 0 || groups > 65535 || (swiglu && act_pq)) return (int)cudaErrorInvalidValue;
     SkinnyParams p{};
+    p.act_pq = act_pq;
     p.offsets_ready = group_offsets && offsets_ready ? 1 : 0;
     p.W = (const bf16*)W; p.w_group_stride = w_group_stride; p.A = (const bf16*)A; p.lda = lda; p.a_rows = a_rows;
     p.group_offsets = group_offsets; p.row_scale = row_scale; p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K;

@@ -6,7 +6,7 @@ import torch
 
 from ..csrc import ops
 from .base import ParamSpec, Part, register
-from .linear import grouped_linear, grouped_swiglu_linear, grouped_uses_tc05, linear, swiglu_linear
+from .linear import grouped_linear, grouped_swiglu_linear, grouped_uses_tc05, linear, swiglu_linear, xielu_linear
 
 
 class DeferredMoeCombine:
@@ -116,10 +116,8 @@ class DenseXielu(Part):
         step = rt.ffn_chunk_tokens
         for a in range(0, n, step):
             b = min(n, a + step)
-            z = rt.ws.get("xielu_z", (b - a, s.intermediate), torch.float32)
-            linear(rt, h[a:b], self.w_up, z)
             act = rt.ws.get("xielu_act", (b - a, s.intermediate), rt.dtype)
-            ops.xielu(z, self.pq, act)
+            xielu_linear(rt, h[a:b], self.w_up, self.pq, act, "xielu")
             linear(rt, act, self.w_down, y[a:b])
         return y
 

@@ -4,13 +4,14 @@ the cache's per-slot state rows, is zeroed when the slot is opened, and every st
 left there, whatever run of tokens it brings.  Both run on ``ops.gated_scan``, which makes the gates from the projections' raw outputs."""
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..cache import StateSpec
 from ..csrc import ops
 from ..errors import Unsupported
 from .base import ParamSpec, Part, register
-from .linear import linear
+from .linear import SKINNY_ROWS, linear
 
 
 # Steps with more rows than this per sequence make the gates in a parallel pass ahead of the recurrence; shorter
@@ -144,6 +145,13 @@ class DecayBonusRecurrence(Part):
     def kv_layout(self):
         return None
 
+    # the four projections of a short step are one grouped weight-streaming product: rows [mix, token], one group a mix
+    def step_arrays_key(self):
+        return ("token_shift_groups",)
+
+    def step_arrays(self, step):
+        return {"token_shift.group_offsets4": np.arange(5, dtype=np.int32) * step.n_tokens}
+
     def state_spec(self):
         # the heads' matrices, then the row before the sequence's next token
         return StateSpec((self.state_words + self.spec.hidden,), torch.float32)
@@ -156,8 +164,14 @@ class DecayBonusRecurrence(Part):
         ops.token_shift_mix(h, prev, ctx.tok_seq, ctx.seq_start, ctx.seq_slot, self.mu, mixed)
         ops.token_shift_keep(h, prev, ctx.seq_start, ctx.seq_slot, ctx.n_seqs)
         proj = rt.ws.get("wkv_proj", (5, n, self.kw), torch.float32)      # r, k, v, gate, raw decay
-        for i in range(4):
-            linear(rt, mixed[i], self.w[i], proj[i])
+        offsets = ctx.arrays.get("token_shift.group_offsets4")
+        if (offsets is not None and n <= SKINNY_ROWS and mixed.dtype == torch.bfloat16 and self.w.dtype == torch.bfloat16
+                and ops.skinny_fits(s.hidden)):
+            ops.gemm_skinny(mixed.view(len(SHIFTS) * n, s.hidden), self.w, proj.view(5 * n, self.kw), group_offsets=offsets,
+                            rows=4 * n, max_rows=n)
+        else:
+            for i in range(4):
+                linear(rt, mixed[i], self.w[i], proj[i])
         inner = rt.ws.get("wkv_decay_inner", (n, s.decay_rank), torch.float32)
         linear(rt, mixed[4], self.w1, inner)
         inner_act = rt.ws.get("wkv_decay_act", (n, s.decay_rank), rt.dtype)

@@ -388,3 +388,21 @@ def test_gates_made_ahead_give_the_same_bits(mode):
         outs.append(out)
         states.append(state)
     assert torch.equal(outs[0], outs[1]) and torch.equal(states[0], states[1])
+
+
+def test_activation_in_the_products_epilogue():
+    """The weight-streaming product with xIELU in its epilogue against the product followed by the activation's kernel."""
+    torch.manual_seed(9)
+    rows, K, N = 5, 96, 200
+    a = torch.randn(rows, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) / math.sqrt(K)).to(torch.bfloat16)
+    pq = torch.tensor([0.4, -0.3], device=DEV)
+    fused = torch.empty(rows, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_skinny(a, w, fused, xielu_pq=pq)
+    z = torch.empty(rows, N, device=DEV)
+    ops.gemm_skinny(a, w, z)
+    two = torch.empty(rows, N, device=DEV, dtype=torch.bfloat16)
+    ops.xielu(z, pq, two)
+    want = plain.xielu(a.double().cpu() @ w.double().cpu().T, 0.4, -0.3)
+    assert float((fused.double().cpu() - want).abs().max()) <= 2 ** -7 * float(want.abs().max())
+    assert float((fused.float() - two.float()).abs().max()) <= 2 ** -7 * float(want.abs().max())
