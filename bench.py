@@ -468,7 +468,7 @@ def dense_qwen2_config(width, ff, layers, vocab):
                 mlp_only_layers=list(range(layers)), max_position_embeddings=8192)
 
 
-def measure_design(torch, raw, prefill_tokens, batches, context, steps, warmup):
+def measure_design(torch, raw, prefill_tokens, batches, context, steps, warmup, clocks):
     """Prefill of one prompt and decode steps of a model with random weights: tokens per second, and device time
     by kind of kernel for one eager prefill and one eager decode step (library products count with the kernel
     that follows them)."""
@@ -491,11 +491,13 @@ def measure_design(torch, raw, prefill_tokens, batches, context, steps, warmup):
         engine.step([StepEntry(s, rng.integers(0, vocab, prefill_tokens).tolist(), [prefill_tokens - 1])])
         engine.close(s)
 
-    ms = timed_steps(torch, prefill_once, max(3, warmup), max(4, steps // 4))
+    with clocks:                              # clocks are sampled while steps are timed, not while models are built
+        ms = timed_steps(torch, prefill_once, max(3, warmup), max(4, steps // 4))
     out["prefill"] = {"tokens": prefill_tokens, "ms": round(ms, 3), "tok_s": round(prefill_tokens / ms * 1e3, 1)}
     launches = ops.launch_count()
     for b in batches:
-        ms, _distinct, slots, _plen = decode_run(torch, engine, b, context, max(3, warmup), steps, vocab, seed=b)
+        with clocks:
+            ms, _distinct, slots, _plen = decode_run(torch, engine, b, context, max(3, warmup), steps, vocab, seed=b)
         out[f"decode_b{b}"] = {"ms": round(ms, 4), "tok_s": round(b / ms * 1e3, 1)}
         for s in slots:
             engine.close(s)
@@ -526,15 +528,14 @@ def bench_design(torch, a, pk):
               "data": "synthetic token ids, random weights N(0,0.02)", "prefill_tokens": a.prefill_tokens,
               "context": a.context, "steps": a.steps, "warmup": max(3, a.warmup), "peaks": pk, "sizes": {}}
     clocks = ClockSampler()
-    with clocks:
-        for name in picked:
-            width, ff, layers = sizes[name]
-            entry = {"width": width, "ff": ff, "layers": layers, "vocab": vocab}
-            entry["zusepel"] = measure_design(torch, zusepel_config(width, ff, layers, vocab, window), a.prefill_tokens, (1, 8),
-                                              a.context, a.steps, a.warmup)
-            entry["qwen2_dense"] = measure_design(torch, dense_qwen2_config(width, ff, layers, vocab), a.prefill_tokens,
-                                                  (1, 8), a.context, a.steps, a.warmup)
-            result["sizes"][name] = entry
+    for name in picked:
+        width, ff, layers = sizes[name]
+        entry = {"width": width, "ff": ff, "layers": layers, "vocab": vocab}
+        entry["zusepel"] = measure_design(torch, zusepel_config(width, ff, layers, vocab, window), a.prefill_tokens, (1, 8),
+                                          a.context, a.steps, a.warmup, clocks)
+        entry["qwen2_dense"] = measure_design(torch, dense_qwen2_config(width, ff, layers, vocab), a.prefill_tokens,
+                                              (1, 8), a.context, a.steps, a.warmup, clocks)
+        result["sizes"][name] = entry
     result["clocks"] = clocks.summary()
     print(json.dumps(result))
     return 0
