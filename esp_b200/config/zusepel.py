@@ -70,8 +70,25 @@ class ZusepelConfig:
         layers = raw.get("layers")
         if not isinstance(layers, list) or not layers:
             raise InvalidConfig("layers must be a non-empty list")
+        layers = [dict(l, mixer=dict(l["mixer"])) if isinstance(l, dict) and isinstance(l.get("mixer"), dict) else l
+                  for l in layers]
+        if not all(isinstance(l, dict) for l in layers):
+            raise InvalidConfig("every entry of layers must be an object")
+        for i, layer in enumerate(layers):
+            mix = layer.get("mixer")
+            if not isinstance(mix, dict):
+                continue
+            if "vdim" not in mix and "dim" in mix and layer.get("type") in ("hgrn2", "latent_attention"):
+                mix["vdim"] = mix["dim"]                   # value channels default to the key channels
+            src = mix.get("kv_from")
+            if layer.get("type") == "latent_attention" and isinstance(src, int) and not isinstance(src, bool) and 0 <= src < i:
+                owner = layers[src].get("mixer")
+                if isinstance(owner, dict):                # what a reader must share with the cache's owner may be left out
+                    for key in ("kv_rank", "rot_dim", "rot"):
+                        if key not in mix and key in owner:
+                            mix[key] = owner[key]
         cfg = cls(vocab=_int(raw, "vocab", "config"), width=_int(raw, "width", "config"), eps=_num(norm, "eps", "norm"),
-                  residual_mult=_num(raw, "residual_mult", "config"), layers=[dict(l) for l in layers],
+                  residual_mult=_num(raw, "residual_mult", "config") if "residual_mult" in raw else 1.0, layers=layers,
                   decay_ranks={int(k): int(v) for k, v in (raw.get("decay_ranks") or {}).items()})
         cfg.validate()
         return cfg

@@ -24,10 +24,6 @@ def softplus(z):
     return math.log1p(math.exp(z)) if z < 30 else z
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def xielu(z, p, q):
     """p, q: the two raw numbers of the activation."""
     ap, aq = softplus(float(p)), 0.5 + softplus(float(q))

@@ -75,7 +75,7 @@ def _broken(change):
     (lambda r: r["layers"][1]["mixer"].pop("scale"), InvalidConfig),
     (lambda r: r.pop("norm"), InvalidConfig),
     (lambda r: r.update(width=0), InvalidConfig),
-    (lambda r: r["layers"][2]["mixer"].pop("vdim"), InvalidConfig),
+    (lambda r: r["layers"][2]["mixer"].pop("dim"), InvalidConfig),
 ])
 def test_refusals(change, error):
     with pytest.raises(error):
@@ -124,3 +124,14 @@ def test_plain_prefix_property():
     a = plain.forward(raw, w, toks)
     b = plain.forward(raw, w, toks[:-7])
     assert float((a[:-7] - b).abs().max()) < 1e-10      # sums of other lengths may differ in their last bits
+
+
+def test_a_reader_may_leave_out_what_it_shares_with_the_owner():
+    raw = copy.deepcopy(CASE_A)
+    for key in ("kv_rank", "rot_dim", "rot"):
+        raw["layers"][3]["mixer"].pop(key)
+    raw.pop("residual_mult")
+    cfg = config_from_dict(raw)
+    full = config_from_dict(copy.deepcopy(CASE_A))
+    assert cfg.plan().blocks[3].mixer == full.plan().blocks[3].mixer
+    assert cfg.residual_mult == 1.0
