@@ -65,6 +65,13 @@ class KvLayout:
     head_dim: int
     window: Optional[int] = None     # None: keep every position
     values: bool = True              # False: one pool of rows only (a layer whose values are part of its key rows)
+    value_dim: Optional[int] = None  # size of a value head where it differs from a key head's
+
+    @property
+    def row_elements(self) -> int:
+        """Elements that one position of one layer holds (keys and, if kept, values of all heads)."""
+        per_head = self.head_dim + ((self.value_dim or self.head_dim) if self.values else 0)
+        return self.num_kv_heads * per_head
 
 
 class GroupBook:

@@ -37,7 +37,10 @@ class Cache:
     """``requests``: one (KvLayout or None, StateSpec or None, cache_of or None)
     per schedule entry, in schedule order."""
 
-    def __init__(self, requests: list, max_tokens: int, max_slots: int, max_positions: int, dtype, device):
+    def __init__(self, requests: list, max_tokens: int, max_slots: int, max_positions: int, dtype, device,
+                 model_states: Optional[dict] = None):
+        """``model_states``: name -> StateSpec of per-sequence state that belongs to no layer (what the model's
+        embedding keeps, for instance); found again as ``self.named_state[name]``, zeroed when a slot is opened."""
         self.device = device
         self.dtype = dtype
         layouts, members = [], []
@@ -64,8 +67,11 @@ class Cache:
         for layout, m in zip(layouts, members):
             shape = (len(m), n_pages, layout.num_kv_heads, PAGE, layout.head_dim)
             self.k_pools.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device) if layout.values else None)
+            v_shape = (*shape[:-1], layout.value_dim or layout.head_dim)
+            self.v_pools.append(torch.zeros(v_shape, dtype=dtype, device=device) if layout.values else None)
         self.engine_state = torch.zeros((max_slots, STATE_WORDS), dtype=torch.int64, device=device)
+        self.named_state = {name: torch.zeros((max_slots, *spec.shape), dtype=spec.dtype, device=device)
+                            for name, spec in (model_states or {}).items()}
         self.layers = []
         for idx, (layout, state, cache_of) in enumerate(requests):
             st = None
@@ -83,6 +89,8 @@ class Cache:
     def open(self) -> int:
         slot = self.book.open()
         self.engine_state[slot].zero_()
+        for state in self.named_state.values():
+            state[slot].zero_()
         for layer in self.layers:
             if layer.state is not None:
                 layer.state[slot].zero_()
@@ -98,8 +106,7 @@ class Cache:
 
     def bytes_per_token(self) -> int:
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum((2 if l.values else 1) * len(m) * l.num_kv_heads * l.head_dim * el
-                   for l, m in zip(self.layouts, self.members))
+        return sum(len(m) * l.row_elements * el for l, m in zip(self.layouts, self.members))
 
     def state_bytes(self) -> int:
         """Bytes of the mixers' per-sequence states over all slots."""

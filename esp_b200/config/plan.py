@@ -231,6 +231,156 @@ class DepthMixBlockSpec:
 
 
 @dataclass(frozen=True)
+class HashedBigramSpec:
+    """A second table whose row is a hash of the token and the token before it:
+    row = (previous * mul_prev + token * mul_cur) mod buckets; a sequence's first token reads row ``buckets``
+    (the table has buckets + 1 rows)."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    weight: str
+
+
+@dataclass(frozen=True)
+class SummedEmbeddingSpec:
+    """What enters the residual stream: the token's row, plus (optionally) a hashed bigram row and a sinusoidal
+    position vector (entry 2i sin(p b^(-2i/width)), entry 2i + 1 its cosine)."""
+    width: int
+    bigram: Optional[HashedBigramSpec] = None
+    sinusoid_base: Optional[float] = None
+    kind: str = "summed"
+
+
+@dataclass(frozen=True)
+class QueryTemperature:
+    """Queries at position p are multiplied by 1 + coef ln(floor((p + 1) / every) + 1)."""
+    coef: float
+    every: int
+
+
+@dataclass(frozen=True)
+class NormedAttentionNames:
+    """Tensor names of an attention layer with query/key norms, after the spec's prefix; a bias is the
+    projection's name + ``bias``."""
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    o: str = "o"
+    bias: str = ".b"
+    q_norm: str = "q.norm"
+    k_norm: str = "k.norm"
+
+
+@dataclass(frozen=True)
+class NormedAttentionSpec:
+    """Causal softmax attention without rotation: queries and keys get an RMS norm per head (one weight vector for
+    all heads), keys and values may have different sizes, the scores are multiplied by ``scale`` as given, and
+    with ``sink`` the softmax's denominator holds one more term exp(0) that carries no value."""
+    hidden: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    qkv_bias: bool
+    sink: bool
+    q_temp: Optional[QueryTemperature]
+    window: Optional[int]
+    prefix: str
+    kind: str = "attention_qknorm"
+    names: NormedAttentionNames = NormedAttentionNames()
+
+
+@dataclass(frozen=True)
+class MatrixMemoryNames:
+    q: str = "q"
+    k: str = "k"
+    v: str = "v"
+    o: str = "o"
+    gate: str = "g"
+    norm: str = "norm"
+    input_gate: str = "i"            # its bias is the name + ".b"
+    forget_gate: str = "f"
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec:
+    """Matrix memory with an exponential input gate and a sigmoid forget gate, both soft-capped, kept in range by
+    a running maximum m (m_0 = 0):  m_t = max(f_t + m_(t-1), i_t);  S_t = e^(f_t + m_(t-1) - m_t) S_(t-1) +
+    e^(i_t - m_t) k_t v_t^T, n_t likewise with k_t alone;  o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6);
+    each head's o is scaled to unit root mean square, then a weight per channel and a sigmoid gate."""
+    hidden: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    eps: float
+    prefix: str
+    kind: str = "mlstm"
+    names: MatrixMemoryNames = MatrixMemoryNames()
+
+
+@dataclass(frozen=True)
+class GatedDiagonalNames:
+    gate_branch: str = "y"           # biases: the name + ".b"
+    in_branch: str = "x"
+    conv: str = "conv"
+    recurrence_gate: str = "ra"
+    input_gate: str = "ri"
+    decay: str = "lam"
+    o: str = "o"
+
+
+@dataclass(frozen=True)
+class GatedDiagonalSpec:
+    """Two branches of ``channels``: a GELU gate, and a causal convolution of ``taps`` per channel followed by a
+    diagonal recurrence whose decay a_t = exp(-c r_t softplus(lam)) and input gate come from block-diagonal
+    projections of the convolution's output:  S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t."""
+    hidden: int
+    channels: int
+    blocks: int
+    taps: int
+    decay_scale: float               # c above
+    prefix: str
+    kind: str = "rglru"
+    names: GatedDiagonalNames = GatedDiagonalNames()
+
+
+@dataclass(frozen=True)
+class ScaledInputMoeSpec:
+    """Sigmoid router; the ``top_k`` experts with the largest scores; a chosen expert's score multiplies its
+    input; experts are down(act(up x)) with ``activation`` ("relu2": the square of relu); an optional shared
+    expert of the same form takes every token."""
+    hidden: int
+    num_experts: int
+    top_k: int
+    expert_intermediate: int
+    shared_intermediate: Optional[int]
+    prefix: str
+    activation: str = "relu2"
+    kind: str = "moe_sigmoid_scaled_input"
+    router: str = "router"
+    expert: str = "e{e}."
+    shared: str = "shared."
+    up: str = "up"
+    down: str = "down"
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """x += norm_after(mixer(norm_before(x))); x += norm_after(ffn(norm_before(x))): every sublayer's result is
+    normalised before it joins the residual stream.  ``ffn`` None: the layer has a mixer only."""
+    mixer: Any
+    ffn: Any
+    mixer_norm: NormSpec
+    mixer_post_norm: NormSpec
+    ffn_norm: Optional[NormSpec]
+    ffn_post_norm: Optional[NormSpec]
+    kind: str = "sandwich_residual"
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: which parts it has and how they are arranged."""
     mixer: Any                       # any spec object with a ``kind``
@@ -267,3 +417,4 @@ class ModelPlan:
     embed_scale: float = 1.0                 # the table's rows are multiplied by this as they enter the residual stream
     logit_softcap: Optional[float] = None    # logits = cap * tanh(logits / cap)
     tied_head_name: Optional[str] = None     # with head_weight None: a checkpoint may still carry the head under this name
+    embedding: Any = None                    # None: the token's row alone; else a spec of the ``embedding`` family

@@ -10,8 +10,10 @@
 //
 // The new keys and values are already in the cache when this runs, so a step
 // that continues a sequence (past > 0) and a first step are the same case.
-// Head sizes up to HDB (64 or 128) are padded with zeros to HDB in shared
-// memory; they must be multiples of 8.  The page size is 64.
+// Key heads up to HDK and value heads up to HDV (64 or 128 each; keys and values may differ in size) are padded
+// with zeros to that in shared memory; both must be multiples of 8.  The page size is 64.  The scores are
+// dot / sqrt(hd), or dot * scale when a scale is given.  With ``sink`` the softmax's denominator holds one more
+// term, a key of score zero without a value: the running maximum starts at 0 and the running sum at 1.
 #include "common.cuh"
 
 namespace {
@@ -46,18 +48,19 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *reinterpret_cast<unsigned*>(&v);
 }
 
-template <int HDB>
+template <int HDK, int HDV>
 __global__ void __launch_bounds__(THREADS, 3)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                     bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_first,
                     const int* __restrict__ seq_start, const int* __restrict__ seq_past,
                     const int* __restrict__ block_table, int table_stride, int n_pages, int nh, int nkv, int hd,
-                    int window, int* __restrict__ status) {
-    constexpr int LDS = HDB + 8;                     // row stride in elements: 16 bytes of padding against bank conflicts
-    constexpr int PIECES = HDB / 8;
+                    int vd, float scale, int sink, int window, int* __restrict__ status) {
+    constexpr int LDS = HDK + 8;                     // row stride in elements: 16 bytes of padding against bank conflicts
+    constexpr int LDV = HDV + 8;
+    constexpr int PIECES = HDK / 8, VPIECES = HDV / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* k_s = reinterpret_cast<bf16*>(smem_raw);                    // [2][BN][LDS]
-    bf16* v_s = k_s + 2 * BN * LDS;                                    // [2][BN][LDS]
+    bf16* v_s = k_s + 2 * BN * LDS;                                    // [2][BN][LDV]
     bf16* q_s = k_s + BN * LDS;                                        // [BM][LDS]: the tile's queries borrow the second
                                                                        // key buffer until their fragments are in registers
 
@@ -72,7 +75,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
     const int pos_last = pos0 + rows - 1;
     const int kvh = h / (nh / nkv);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tg = lane & 3;
-    const int hd_pieces = hd / 8;
+    const int hd_pieces = hd / 8, vd_pieces = vd / 8;
 
     // ---- the tile's queries -> shared memory (rows beyond the tile and columns beyond hd are zero)
     for (int idx = tid; idx < BM * PIECES; idx += THREADS) {
@@ -93,13 +96,16 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
             pg = 0;
         }
         const bf16* kp = k_cache + ((size_t)pg * nkv + kvh) * BN * hd;
-        const bf16* vp = v_cache + ((size_t)pg * nkv + kvh) * BN * hd;
+        const bf16* vp = v_cache + ((size_t)pg * nkv + kvh) * BN * vd;
         for (int idx = tid; idx < BN * PIECES; idx += THREADS) {
             const int r = idx / PIECES, p = idx - r * PIECES;
             const bool ok = pg_ok && p < hd_pieces;
-            const size_t off = (size_t)r * hd + (ok ? p : 0) * 8;
-            cp_async16(k_s + (buf * BN + r) * LDS + p * 8, kp + off, ok);
-            cp_async16(v_s + (buf * BN + r) * LDS + p * 8, vp + off, ok);
+            cp_async16(k_s + (buf * BN + r) * LDS + p * 8, kp + (size_t)r * hd + (ok ? p : 0) * 8, ok);
+        }
+        for (int idx = tid; idx < BN * VPIECES; idx += THREADS) {
+            const int r = idx / VPIECES, p = idx - r * VPIECES;
+            const bool ok = pg_ok && p < vd_pieces;
+            cp_async16(v_s + (buf * BN + r) * LDV + p * 8, vp + (size_t)r * vd + (ok ? p : 0) * 8, ok);
         }
         cp_async_commit();
     };
@@ -108,18 +114,22 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
     // ---- query fragments of this warp's 16 rows stay in registers
     cp_async_wait<1>();
     __syncthreads();
-    unsigned qf[HDB / 16][4];
+    unsigned qf[HDK / 16][4];
 #pragma unroll
-    for (int kk = 0; kk < HDB / 16; kk++)
+    for (int kk = 0; kk < HDK / 16; kk++)
         ldmatrix_x4(qf[kk], q_s + (warp * 16 + (lane & 15)) * LDS + kk * 16 + (lane >> 4) * 8);
     __syncthreads();                                                   // the borrowed buffer may now be refilled with keys
 
-    float o[HDB / 8][4];
+    float o[HDV / 8][4];
 #pragma unroll
-    for (int i = 0; i < HDB / 8; i++)
+    for (int i = 0; i < HDV / 8; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) o[i][j] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    if (sink) {
+        m_run[0] = m_run[1] = 0.f;
+        if (tg == 0) l_run[0] = l_run[1] = 1.f;      // the sums of a row's four lanes are added at the end: one of them holds the sink
+    }
     const float root = sqrtf((float)hd);
     const float log2e = 1.4426950408889634f;
     const int my_pos[2] = {pos0 + warp * 16 + g, pos0 + warp * 16 + g + 8};   // absolute positions of this lane's two rows
@@ -130,7 +140,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
         if (blk < blk_hi) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncthreads();
         const bf16* kb = k_s + buf * BN * LDS;
-        const bf16* vb = v_s + buf * BN * LDS;
+        const bf16* vb = v_s + buf * BN * LDV;
 
         // S = Q K^T for 16 rows x 64 keys
         float s[BN / 8][4];
@@ -139,7 +149,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
 #pragma unroll
             for (int j = 0; j < 4; j++) s[i][j] = 0.f;
 #pragma unroll
-        for (int kk = 0; kk < HDB / 16; kk++) {
+        for (int kk = 0; kk < HDK / 16; kk++) {
 #pragma unroll
             for (int nb = 0; nb < BN / 16; nb++) {
                 unsigned kf[4];
@@ -159,7 +169,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
             for (int j = 0; j < 4; j++) {
                 const int r = j >> 1;
                 const int key = key0 + nb * 8 + tg * 2 + (j & 1);
-                float v = s[nb][j] / root;
+                float v = scale > 0.f ? s[nb][j] * scale : s[nb][j] / root;
                 if (edge) {
                     const bool seen = key <= my_pos[r] && (window <= 0 || my_pos[r] - key < window);
                     if (!seen) v = -INFINITY;
@@ -191,7 +201,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
 #pragma unroll
         for (int r = 0; r < 2; r++) l_run[r] = l_run[r] * scale_old[r] + l_add[r];
 #pragma unroll
-        for (int i = 0; i < HDB / 8; i++) {
+        for (int i = 0; i < HDV / 8; i++) {
             o[i][0] *= scale_old[0];
             o[i][1] *= scale_old[0];
             o[i][2] *= scale_old[1];
@@ -206,9 +216,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
             pf[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
             pf[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
 #pragma unroll
-            for (int nb = 0; nb < HDB / 16; nb++) {
+            for (int nb = 0; nb < HDV / 16; nb++) {
                 unsigned vf[4];
-                ldmatrix_x4_trans(vf, vb + (kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + nb * 16 + (lane >> 4) * 8);
+                ldmatrix_x4_trans(vf, vb + (kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDV + nb * 16 + (lane >> 4) * 8);
                 mma16816(o[2 * nb], pf, vf[0], vf[1]);
                 mma16816(o[2 * nb + 1], pf, vf[2], vf[3]);
             }
@@ -226,11 +236,11 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
         const int row = warp * 16 + g + r * 8;
         if (row >= rows) continue;
         const float inv = l_run[r] > 0.f ? 1.0f / l_run[r] : 0.f;
-        bf16* orow = out + ((size_t)(row0 + row) * nh + h) * hd;
+        bf16* orow = out + ((size_t)(row0 + row) * nh + h) * vd;
 #pragma unroll
-        for (int i = 0; i < HDB / 8; i++) {
+        for (int i = 0; i < HDV / 8; i++) {
             const int d = i * 8 + tg * 2;
-            if (d < hd) {
+            if (d < vd) {
                 __nv_bfloat162 v = __floats2bfloat162_rn(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
                 *reinterpret_cast<__nv_bfloat162*>(orow + d) = v;
             }
@@ -238,37 +248,44 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache
     }
 }
 
-template <int HDB>
+template <int HDK, int HDV>
 int launch(const bf16* q, const bf16* k, const bf16* v, bf16* out, const int* tile_seq, const int* tile_first,
            const int* seq_start, const int* seq_past, const int* table, int stride, int n_pages, int n_tiles, int nh,
-           int nkv, int hd, int window, int* status, cudaStream_t stream) {
+           int nkv, int hd, int vd, float scale, int sink, int window, int* status, cudaStream_t stream) {
     static_assert(BM <= BN, "the queries borrow a key buffer");
-    const size_t smem = (size_t)(4 * BN) * (HDB + 8) * sizeof(bf16);
+    const size_t smem = (size_t)(2 * BN) * ((HDK + 8) + (HDV + 8)) * sizeof(bf16);
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HDB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<HDK, HDV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         raised = true;
     }
     dim3 grid(n_tiles, nh);
-    attn_prefill_kernel<HDB><<<grid, THREADS, smem, stream>>>(q, k, v, out, tile_seq, tile_first, seq_start, seq_past,
-                                                              table, stride, n_pages, nh, nkv, hd, window, status);
+    attn_prefill_kernel<HDK, HDV><<<grid, THREADS, smem, stream>>>(q, k, v, out, tile_seq, tile_first, seq_start, seq_past,
+                                                                   table, stride, n_pages, nh, nkv, hd, vd, scale, sink,
+                                                                   window, status);
     return esp_launch_status();
 }
 }  // namespace
 
 // tile_seq / tile_first: for every tile of 64 new tokens, its sequence and the index of its first token
-// among that sequence's new tokens.  hd: a multiple of 8, at most 128.  The cache page holds 64 positions.
+// among that sequence's new tokens.  hd (keys) and vd (values; 0: as the keys): multiples of 8, at most 128.
+// scale 0: scores are divided by sqrt(hd).  The cache page holds 64 positions.
 ESP_API int esp_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                              const int* tile_first, const int* seq_start, const int* seq_past, const int* block_table,
-                             int table_stride, int n_pages, int page, int n_tiles, int nh, int nkv, int hd, int window,
-                             int* status, cudaStream_t stream) {
+                             int table_stride, int n_pages, int page, int n_tiles, int nh, int nkv, int hd, int vd,
+                             float scale, int sink, int window, int* status, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
-    if (page != BN || hd % 8 != 0 || hd > 128 || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535)
+    if (vd <= 0) vd = hd;
+    if (page != BN || hd % 8 != 0 || hd > 128 || hd <= 0 || vd % 8 != 0 || vd > 128 || nkv <= 0 || nh % nkv != 0 || nh > 65535)
         return (int)cudaErrorInvalidValue;
-    if (hd <= 64)
-        return launch<64>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, tile_seq, tile_first,
-                          seq_start, seq_past, block_table, table_stride, n_pages, n_tiles, nh, nkv, hd, window, status, stream);
-    return launch<128>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, tile_seq, tile_first,
-                       seq_start, seq_past, block_table, table_stride, n_pages, n_tiles, nh, nkv, hd, window, status, stream);
+#define ESP_FLASH(HDK_, HDV_)                                                                                              \
+    return launch<HDK_, HDV_>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, tile_seq, tile_first, \
+                              seq_start, seq_past, block_table, table_stride, n_pages, n_tiles, nh, nkv, hd, vd, scale, sink, \
+                              window, status, stream)
+    if (hd <= 64 && vd <= 64) ESP_FLASH(64, 64);
+    if (hd <= 64) ESP_FLASH(64, 128);
+    if (vd <= 64) ESP_FLASH(128, 64);
+    ESP_FLASH(128, 128);
+#undef ESP_FLASH
 }

@@ -3,7 +3,9 @@
 // prefill and decode alike and any head size up to 256.
 //
 // The query at absolute position a sees key j iff j <= a and (window == 0 or
-// a - j < window).  score = dot(q, k_j) / sqrt(hd) (divided after the product).
+// a - j < window).  score = dot(q, k_j) / sqrt(hd) (divided after the product), or dot(q, k_j) * scale when a scale is
+// given.  Values may have another size than keys (vd).  With ``sink`` the denominator holds one more term, exp(0 - max):
+// a key of score zero that carries no value.
 // Keys are walked in chunks of CHUNK positions aligned to absolute multiples of
 // CHUNK with a running maximum and sum, so the order of every addition depends
 // on the query's position alone: not on how the sequence was cut into steps,
@@ -20,7 +22,7 @@ __global__ void __launch_bounds__(THREADS)
 attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                  T* __restrict__ out, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                  const int* __restrict__ block_table, int table_stride, int n_pages, int page, int nh, int nkv, int hd,
-                 int window, int* __restrict__ status) {
+                 int vd, float scale, int sink, int window, int* __restrict__ status) {
     __shared__ float qs[MAX_HD];
     __shared__ float ps[CHUNK];
     __shared__ int pages[CHUNK];      // page id of each key of the chunk (or -1)
@@ -32,7 +34,8 @@ attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
     const T* qrow = q + ((size_t)n * nh + h) * hd;
     for (int d = tid; d < hd; d += THREADS) qs[d] = to_f32(qrow[d]);
     const float root = sqrtf((float)hd);
-    float m_run = -INFINITY, l_run = 0.f;
+    // the sink is a key of score zero ahead of all others: the running maximum and sum start from it
+    float m_run = sink ? 0.f : -INFINITY, l_run = sink ? 1.f : 0.f;
     float acc[MAX_HD / THREADS];
 #pragma unroll
     for (int i = 0; i < MAX_HD / THREADS; i++) acc[i] = 0.f;
@@ -56,7 +59,7 @@ attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                 const T* krow = k_cache + (((size_t)pg * nkv + kvh) * page + j % page) * hd;
                 float dot = 0.f;
                 for (int d = 0; d < hd; d++) dot = fmaf(qs[d], to_f32(krow[d]), dot);
-                s = dot / root;
+                s = scale > 0.f ? dot * scale : dot / root;
             }
             ps[t] = s;
             local_max = fmaxf(local_max, s);
@@ -77,42 +80,44 @@ attn_simt_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 #pragma unroll
         for (int i = 0; i < MAX_HD / THREADS; i++) {
             const int d = tid + i * THREADS;
-            if (d < hd) {
+            if (d < vd) {
                 float a = acc[i] * rescale;
                 for (int t = 0; t < count; t++) {
                     const int pg = pages[t];
                     if (pg < 0) continue;
                     const int j = j0 + t;
-                    a = fmaf(ps[t], to_f32(v_cache[(((size_t)pg * nkv + kvh) * page + j % page) * hd + d]), a);
+                    a = fmaf(ps[t], to_f32(v_cache[(((size_t)pg * nkv + kvh) * page + j % page) * vd + d]), a);
                 }
                 acc[i] = a;
             }
         }
         __syncthreads();
     }
-    T* orow = out + ((size_t)n * nh + h) * hd;
+    T* orow = out + ((size_t)n * nh + h) * vd;
 #pragma unroll
     for (int i = 0; i < MAX_HD / THREADS; i++) {
         const int d = tid + i * THREADS;
-        if (d < hd) orow[d] = from_f32<T>(l_run > 0.f ? acc[i] / l_run : 0.f);
+        if (d < vd) orow[d] = from_f32<T>(l_run > 0.f ? acc[i] / l_run : 0.f);
     }
 }
 }  // namespace
 
 ESP_API int esp_attn_simt(const void* q, const void* k_cache, const void* v_cache, void* out, int is_bf16,
                           const int* tok_seq, const int* tok_pos, const int* block_table, int table_stride, int n_pages,
-                          int page, int n_tokens, int nh, int nkv, int hd, int window, int* status, cudaStream_t stream) {
+                          int page, int n_tokens, int nh, int nkv, int hd, int vd, float scale, int sink, int window,
+                          int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (hd > MAX_HD || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535) return (int)cudaErrorInvalidValue;
+    if (vd <= 0) vd = hd;
+    if (vd > MAX_HD || hd > MAX_HD || hd <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid(n_tokens, nh);
     if (is_bf16)
         attn_simt_kernel<bf16><<<grid, THREADS, 0, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                                             (bf16*)out, tok_seq, tok_pos, block_table, table_stride,
-                                                            n_pages, page, nh, nkv, hd, window, status);
+                                                            n_pages, page, nh, nkv, hd, vd, scale, sink, window, status);
     else
         attn_simt_kernel<float><<<grid, THREADS, 0, stream>>>((const float*)q, (const float*)k_cache,
                                                              (const float*)v_cache, (float*)out, tok_seq, tok_pos,
                                                              block_table, table_stride, n_pages, page, nh, nkv, hd,
-                                                             window, status);
+                                                             vd, scale, sink, window, status);
     return esp_launch_status();
 }

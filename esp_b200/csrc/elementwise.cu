@@ -397,3 +397,161 @@ ESP_API int esp_tanh(const float* z, void* out, int out_is_bf16, long long count
         esp_launch_pdl(ESP_PDL_SMALL, tanh_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, (float*)out, count);
     return esp_launch_status();
 }
+
+// ---------------------------------------------------------------- summed embeddings
+// x[n] = table[id] + bigram[row] + position vector.  row = (prev * mul_prev + id * mul_cur) mod buckets, prev being
+// the token before this one in its sequence; a sequence's first token reads row ``buckets``.  The token before a
+// run's first token is the sequence's state (prev_state[slot] holds token + 1; 0: the sequence has no token yet);
+// the block of a run's first token also leaves the run's last token there.  Position vector: entry 2i is
+// sin(p * freq[i]), entry 2i + 1 its cosine, the angle taken in 32-bit.  ``bigram`` and ``freq`` may be null.
+template <typename TW>
+__global__ void embed_sum_kernel(const TW* __restrict__ table, const TW* __restrict__ bigram, const float* __restrict__ freq,
+                                 const int* __restrict__ ids, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                 const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                                 int* __restrict__ prev_state, float* __restrict__ x, int width, int vocab, int buckets,
+                                 long long mul_prev, long long mul_cur, float scale, int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    int id = ids[n];
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, ESP_STATUS_BAD_INDEX);
+        id = 0;
+    }
+    const int seq = tok_seq[n];
+    const bool first = n == seq_start[seq];
+    const TW* brow = nullptr;
+    if (bigram) {
+        int prev;
+        if (first) {
+            prev = prev_state[seq_slot[seq]] - 1;
+        } else {
+            prev = ids[n - 1];
+            if (prev < 0 || prev >= vocab) prev = 0;
+        }
+        const long long row = prev < 0 ? (long long)buckets : ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+        brow = bigram + (size_t)row * width;
+    }
+    const TW* row = table + (size_t)id * width;
+    const float p = (float)tok_pos[n];
+    float* out = x + (size_t)n * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = scale * to_f32(row[i]);
+        if (brow) v += to_f32(brow[i]);
+        if (freq) {
+            const float a = p * freq[i >> 1];
+            v += (i & 1) ? cosf(a) : sinf(a);
+        }
+        out[i] = v;
+    }
+    if (first && bigram) {
+        __syncthreads();                       // the state was read by thread-private code above; one thread writes it
+        if (threadIdx.x == 0) {
+            int last = ids[seq_start[seq + 1] - 1];
+            if (last < 0 || last >= vocab) last = 0;
+            prev_state[seq_slot[seq]] = last + 1;
+        }
+    }
+}
+
+ESP_API int esp_embed_sum(const void* table, const void* bigram, int table_is_bf16, const float* freq, const int* ids,
+                          const int* tok_seq, const int* tok_pos, const int* seq_start, const int* seq_slot, int* prev_state,
+                          float* x, int n_tokens, int width, int vocab, int buckets, long long mul_prev, long long mul_cur,
+                          float scale, int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (bigram && (!prev_state || buckets <= 0)) return (int)cudaErrorInvalidValue;
+    if (table_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, embed_sum_kernel<bf16>, dim3(n_tokens), dim3(256), 0, stream, (const bf16*)table,
+                       (const bf16*)bigram, freq, ids, tok_seq, tok_pos, seq_start, seq_slot, prev_state, x, width, vocab,
+                       buckets, mul_prev, mul_cur, scale, status);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, embed_sum_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, (const float*)table,
+                       (const float*)bigram, freq, ids, tok_seq, tok_pos, seq_start, seq_slot, prev_state, x, width, vocab,
+                       buckets, mul_prev, mul_cur, scale, status);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- norm of a sublayer's result + add + the next norm
+// Row r works on source row s = rows ? rows[r] : r.
+//   d = y[s] / sqrt(mean(y[s]^2) + eps_y) * gamma_y;  v = x[s] + d;  if (write_x) x[s] = v;
+//   h[r] = v / sqrt(mean(v^2) + eps) * gamma     (h null: only the first two lines)
+// All in 32-bit; sums of squares per thread in index order, combined by a fixed tree.  With ``x`` null the kernel
+// writes d itself to ``h32`` (the normed result alone).
+template <typename TH>
+__global__ void norm_add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma_y,
+                                        float eps_y, const float* __restrict__ gamma, const int* __restrict__ rows,
+                                        TH* __restrict__ h, float* __restrict__ h32, int width, float eps, int write_x) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    const float* yr = y + s * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(yr[i], yr[i], ss);
+    const float inv_y = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps_y);
+    if (!x) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) h32[(size_t)r * width + i] = yr[i] * inv_y * gamma_y[i];
+        return;
+    }
+    float* xr = x + s * width;
+    ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i] + yr[i] * inv_y * gamma_y[i];
+        if (write_x) xr[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!h) return;
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    TH* hr = h + (size_t)r * width;
+    float* h32r = h32 ? h32 + (size_t)r * width : nullptr;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = write_x ? xr[i] : xr[i] + yr[i] * inv_y * gamma_y[i];
+        const float o = v * inv * gamma[i];
+        hr[i] = from_f32<TH>(o);
+        if (h32r) h32r[i] = o;
+    }
+}
+
+ESP_API int esp_norm_add_rmsnorm(float* x, const float* y, const float* gamma_y, float eps_y, const float* gamma,
+                                 const int* rows, void* h, int h_is_bf16, float* h32, int n_rows, int width, float eps,
+                                 int write_x, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (!y || !gamma_y || (!x && !h32) || (h && !gamma)) return (int)cudaErrorInvalidValue;
+    const int threads = width >= 2048 ? 512 : width >= 512 ? 256 : 128;
+    if (h_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, norm_add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma_y,
+                       eps_y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, norm_add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma_y,
+                       eps_y, gamma, rows, (float*)h, h32, width, eps, write_x);
+    return esp_launch_status();
+}
+
+// ---------------------------------------------------------------- squared ReLU
+// act[m, i] = max(z[m, i] * (row_scale ? row_scale[m] : 1), 0)^2
+template <typename TO>
+__global__ void relu2_kernel(const float* __restrict__ z, const float* __restrict__ row_scale, TO* __restrict__ act,
+                             long long rows, int width) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = rows * width;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        float v = z[i];
+        if (row_scale) v *= row_scale[i / width];
+        v = fmaxf(v, 0.f);
+        act[i] = from_f32<TO>(v * v);
+    }
+}
+
+ESP_API int esp_relu2(const float* z, const float* row_scale, void* act, int act_is_bf16, long long rows, int width,
+                      cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    long long blocks = (rows * width + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (act_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, relu2_kernel<bf16>, dim3((int)blocks), dim3(256), 0, stream, z, row_scale, (bf16*)act, rows, width);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, relu2_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, z, row_scale, (float*)act, rows, width);
+    return esp_launch_status();
+}

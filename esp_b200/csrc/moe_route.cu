@@ -9,6 +9,42 @@ constexpr int ROUTER_THREADS = 512;
 constexpr int MAX_TOPK = 32;
 constexpr int ROUTE_SMALL_MAX = 64;          // tokens of a step that the two-launch router takes (an expert's rows stay one tile)
 
+// ``norm_topk`` of the entry points is a word of flags.
+enum : int {
+    ROUTE_RENORM = 1,     // the chosen experts' scores are divided by their sum
+    ROUTE_SIGMOID = 2,    // scores are sigmoid(logit), each expert by itself, instead of a softmax over all experts
+};
+
+// A token's scores from its logits, by one warp: ps[e] = softmax(lg)[e], or sigmoid(lg[e]).  lg and ps may be the same
+// array.  ``probs`` (may be null) receives a copy.
+__device__ __forceinline__ void scores_from_logits(const float* lg, float* ps, int n_experts, int lane, int sigmoid,
+                                                   float* probs) {
+    if (sigmoid) {
+        for (int e = lane; e < n_experts; e += 32) {
+            const float p = 1.0f / (1.0f + expf(-lg[e]));
+            ps[e] = p;
+            if (probs) probs[e] = p;
+        }
+        return;
+    }
+    float mx = -INFINITY;
+    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, lg[e]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < n_experts; e += 32) {
+        const float p = expf(lg[e] - mx);
+        ps[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < n_experts; e += 32) {
+        const float p = ps[e] / sum;
+        ps[e] = p;
+        if (probs) probs[e] = p;
+    }
+}
+
 // A lane's share of dot(hs[t], w) for TPB token rows at once: 4 consecutive
 // weights at a time (8-byte loads of bfloat16, 16-byte of float), lanes
 // interleaved so that the float4 reads of hs fall into distinct banks, several
@@ -131,22 +167,7 @@ router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, co
     for (int t = warp; t < live; t += nwarp) {
         const int n = n0 + t;
         float* ps = ps_all + t * n_experts;
-        float mx = -INFINITY;
-        for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, ps[e]);
-        mx = warp_max(mx);
-        float sum = 0.f;
-        for (int e = lane; e < n_experts; e += 32) {
-            const float p = expf(ps[e] - mx);
-            ps[e] = p;
-            sum += p;
-        }
-        sum = warp_sum(sum);
-        __syncwarp();
-        for (int e = lane; e < n_experts; e += 32) {
-            const float p = ps[e] / sum;
-            ps[e] = p;
-            if (probs_out) probs_out[(size_t)n * n_experts + e] = p;
-        }
+        scores_from_logits(ps, ps, n_experts, lane, norm_topk & ROUTE_SIGMOID, probs_out ? probs_out + (size_t)n * n_experts : nullptr);
         __syncwarp();
         // top-k by repeated arg-max (k and E are small); ties go to the lower id; rank r is kept by lane r
         bool bad = false;
@@ -172,7 +193,7 @@ router_topk_kernel(const TH* __restrict__ h, const TW* __restrict__ w_router, co
             mass += best;
             __syncwarp();
         }
-        const float denom = norm_topk ? mass : 1.0f;
+        const float denom = (norm_topk & ROUTE_RENORM) ? mass : 1.0f;
         if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
             if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
         }
@@ -288,22 +309,7 @@ router_select_kernel(const float* __restrict__ logits, int* __restrict__ topk_id
     if (n >= n_tokens) return;
     float* ps = sel_ps + warp * n_experts;
     const float* lg = logits + (size_t)n * (n_experts + 1);
-    float mx = -INFINITY;
-    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, lg[e]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < n_experts; e += 32) {
-        const float p = expf(lg[e] - mx);
-        ps[e] = p;
-        sum += p;
-    }
-    sum = warp_sum(sum);
-    __syncwarp();
-    for (int e = lane; e < n_experts; e += 32) {
-        const float p = ps[e] / sum;
-        ps[e] = p;
-        if (probs_out) probs_out[(size_t)n * n_experts + e] = p;
-    }
+    scores_from_logits(lg, ps, n_experts, lane, norm_topk & ROUTE_SIGMOID, probs_out ? probs_out + (size_t)n * n_experts : nullptr);
     if (lane == 0 && has_gate) gate[n] = 1.0f / (1.0f + expf(-lg[n_experts]));
     __syncwarp();
     bool bad = false;
@@ -329,7 +335,7 @@ router_select_kernel(const float* __restrict__ logits, int* __restrict__ topk_id
         mass += best;
         __syncwarp();
     }
-    const float denom = norm_topk ? mass : 1.0f;
+    const float denom = (norm_topk & ROUTE_RENORM) ? mass : 1.0f;
     if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
         if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
     }
@@ -389,22 +395,7 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
     float* ps = ps_all + warp * n_experts;
     for (int n = warp; n < n_tokens; n += 8) {
         const float* lg = logits + (size_t)n * (n_experts + 1);
-        float mx = -INFINITY;
-        for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, lg[e]);
-        mx = warp_max(mx);
-        float sum = 0.f;
-        for (int e = lane; e < n_experts; e += 32) {
-            const float p = expf(lg[e] - mx);
-            ps[e] = p;
-            sum += p;
-        }
-        sum = warp_sum(sum);
-        __syncwarp();
-        for (int e = lane; e < n_experts; e += 32) {
-            const float p = ps[e] / sum;
-            ps[e] = p;
-            if (probs_out) probs_out[(size_t)n * n_experts + e] = p;
-        }
+        scores_from_logits(lg, ps, n_experts, lane, norm_topk & ROUTE_SIGMOID, probs_out ? probs_out + (size_t)n * n_experts : nullptr);
         if (lane == 0 && has_gate) gate[n] = 1.0f / (1.0f + expf(-lg[n_experts]));
         __syncwarp();
         bool bad = false;
@@ -430,7 +421,7 @@ route_small_kernel(const float* __restrict__ logits, int* __restrict__ topk_ids,
             mass += best;
             __syncwarp();
         }
-        const float denom = norm_topk ? mass : 1.0f;
+        const float denom = (norm_topk & ROUTE_RENORM) ? mass : 1.0f;
         if (__any_sync(0xffffffffu, bad) || !(denom > 0.f)) {
             if (lane == 0) atomicOr(status, ESP_STATUS_ROUTER_NONFINITE);
         }
@@ -668,7 +659,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ expert_out, const i
         for (int r = 0; r < top_k; r++) order[r] = inverse[(size_t)t * top_k + order[r]];
     }
     __syncthreads();
-    const float g = gate ? gate[t] : 0.f;
+    const float g = gate ? gate[t] : 1.0f;       // no gate: the shared rows are added as they are
     if ((width & 3) == 0) {
         // four columns per thread; each column still adds its terms in the same order
         for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
@@ -731,7 +722,7 @@ moe_combine_add_rmsnorm_kernel(const float* __restrict__ expert_out, const int* 
         }
         for (int j = 0; j < top_k; j++) order[j] = inverse[t * top_k + order[j]];
     }
-    const float g = gate ? gate[t] : 0.f;
+    const float g = gate ? gate[t] : 1.0f;       // no gate: the shared rows are added as they are
     const int pieces = width / 4;
     float4 v[4];
 #pragma unroll

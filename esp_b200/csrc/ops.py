@@ -46,7 +46,18 @@ _SIGNATURES = {
     "esp_gemm_simt": [P, c_int, P, P, c_int, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, P],
     "esp_rope_kvwrite": [P, P, P, P, P, P, c_int, c_int, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_int, c_int, P, P],
-    "esp_attn_simt": [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_attn_simt": [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                      P, P],
+    "esp_embed_sum": [P, P, c_int, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_float, P, P],
+    "esp_norm_add_rmsnorm": [P, P, P, c_float, P, P, P, c_int, P, c_int, c_int, c_float, c_int, P],
+    "esp_relu2": [P, P, P, c_int, c_longlong, c_int, P],
+    "esp_qknorm_kvwrite": [P, P, P, P, c_float, c_float, c_int, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_int, P, P],
+    "esp_matrix_memory_prepare": [P, P, P, P, P, c_longlong, P, P, c_float, c_float, P, c_longlong, P, P, P, P, P, P, P, c_int,
+                                  c_int, c_int, c_int, c_int, P],
+    "esp_matrix_memory_finish": [P, P, P, P, c_longlong, P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, P],
+    "esp_conv_branches": [P, P, P, P, P, P, c_longlong, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
+    "esp_diag_scan": [P, P, P, P, c_float, P, P, P, c_longlong, P, P, P, c_int, c_int, c_int, c_int, P],
     "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
@@ -62,7 +73,8 @@ _SIGNATURES = {
                         c_int, c_int, P, P],
     "esp_qkv_rope_skinny": [P, c_longlong, P, P, P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_int, c_int, c_int, P, P],
-    "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+    "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                         c_int, P, P],
     "esp_attn_prefill_tc05": [P, c_longlong, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               P, P],
     "esp_attn_decode": [P, P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -319,18 +331,23 @@ def rope_kvwrite(qkv, bias, tok_seq, tok_pos, cos, sin, rot, q_out, k_cache, v_c
         nh, nkv, hd, 1 if write_kv else 0, _ptr(status, torch.int32), _stream()), "rope_kvwrite")
 
 
-def attn_simt(q, k_cache, v_cache, out, tok_seq, tok_pos, block_table, page, nh, nkv, hd, window, status):
-    """Attention of every token over its sequence's cached keys (32-bit arithmetic)."""
-    if hd > 256:
-        raise Backend(f"attention: head size {hd} is beyond the 256 this kernel takes")
+def attn_simt(q, k_cache, v_cache, out, tok_seq, tok_pos, block_table, page, nh, nkv, hd, window, status, vd=None,
+              scale=0.0, sink=False):
+    """Attention of every token over its sequence's cached keys (32-bit arithmetic).  ``vd``: size of a value head
+    (default: the key size); ``scale`` > 0 multiplies the scores instead of the division by sqrt(hd); ``sink``: the
+    softmax's denominator holds one more term exp(0)."""
+    vd = hd if vd is None else vd
+    if hd > 256 or vd > 256:
+        raise Backend(f"attention: head sizes {hd} / {vd} are beyond the 256 this kernel takes")
     _check(_fn("core", "esp_attn_simt")(
         _ptr(q, FLOATS, "q"), _ptr(k_cache, FLOATS), _ptr(v_cache, FLOATS), _ptr(out, FLOATS), _is_bf16(q),
         _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(block_table, torch.int32), block_table.shape[1],
-        k_cache.shape[0], page, q.shape[0], nh, nkv, hd, int(window or 0), _ptr(status, torch.int32), _stream()),
-        "attn_simt")
+        k_cache.shape[0], page, q.shape[0], nh, nkv, hd, vd, float(scale), 1 if sink else 0, int(window or 0),
+        _ptr(status, torch.int32), _stream()), "attn_simt")
 
 
-def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, status, probs_out=None, logits=None):
+def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, status, probs_out=None, logits=None,
+                sigmoid=False):
     """``logits``: optional float32 scratch [n, experts + 1]; with it, 32-bit activations and bfloat16 weights
     the logits of a step of many tokens are made on the tensor cores (three bfloat16 parts of every
     activation: products exact, sums in float)."""
@@ -347,8 +364,8 @@ def router_topk(h, w_router, w_gate, topk_ids, topk_w, gate, top_k, norm_topk, s
     _check(_fn("core", "esp_router_topk")(
         _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(w_router, FLOATS), _ptr(w_gate, FLOATS), _is_bf16(w_router),
         _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32), _ptr(gate, torch.float32),
-        _ptr(probs_out, torch.float32), _ptr(logits, torch.float32), n, width, n_experts, top_k, 1 if norm_topk else 0,
-        _ptr(status, torch.int32), _stream()), "router_topk")
+        _ptr(probs_out, torch.float32), _ptr(logits, torch.float32), n, width, n_experts, top_k,
+        (1 if norm_topk else 0) | (2 if sigmoid else 0), _ptr(status, torch.int32), _stream()), "router_topk")
 
 
 ROUTE_SMALL_TOKENS = 64
@@ -360,7 +377,7 @@ def route_small_fits(width: int, n_experts: int) -> bool:
 
 
 def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm_topk, offsets, perm_token,
-                perm_weight, inverse, status, probs_out=None, distinct=None, tiles=None):
+                perm_weight, inverse, status, probs_out=None, distinct=None, tiles=None, sigmoid=False):
     """Router and permutation for at most ROUTE_SMALL_TOKENS tokens: logits over many blocks, then one
     block for softmax, top-k and the permutation.  ``logits``: float32 scratch [N, E + 1].  ``distinct``:
     an int64 tensor of one element to which the number of experts with at least one token is added.
@@ -372,8 +389,8 @@ def route_small(h, w_router, w_gate, logits, topk_ids, topk_w, gate, top_k, norm
     _check(_fn("core", "esp_route_small")(
         _ptr(h, FLOATS, "h"), _is_bf16(h), _ptr(w_router, FLOATS), _ptr(w_gate, FLOATS), _is_bf16(w_router),
         _ptr(logits, torch.float32), _ptr(topk_ids, torch.int32), _ptr(topk_w, torch.float32),
-        _ptr(gate, torch.float32), _ptr(probs_out, torch.float32), n, width, n_experts, top_k, 1 if norm_topk else 0,
-        _ptr(offsets, torch.int32), _ptr(perm_token, torch.int32), _ptr(perm_weight, torch.float32),
+        _ptr(gate, torch.float32), _ptr(probs_out, torch.float32), n, width, n_experts, top_k,
+        (1 if norm_topk else 0) | (2 if sigmoid else 0), _ptr(offsets, torch.int32), _ptr(perm_token, torch.int32), _ptr(perm_weight, torch.float32),
         _ptr(inverse, torch.int32), _ptr(status, torch.int32), _ptr(distinct, torch.int64),
         _ptr(tiles[0], torch.int32) if tiles else None, _ptr(tiles[1], torch.int32) if tiles else None,
         _ptr(tiles[2], torch.int32) if tiles else None, _ptr(tiles[3], torch.int32) if tiles else None,
@@ -557,18 +574,27 @@ def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, to
         _stream()), "attn_decode")
 
 
+def attn_flash_fits(hd, vd=None, page=64) -> bool:
+    """Head sizes (keys, values) and page size that ``attn_prefill`` takes."""
+    vd = hd if vd is None else vd
+    return hd % 8 == 0 and vd % 8 == 0 and 0 < hd <= 128 and 0 < vd <= 128 and page == 64
+
+
 def attn_prefill(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, nh, nkv, hd,
-                 window, status):
+                 window, status, vd=None, scale=0.0, sink=False):
     """Flash-style attention for runs of new tokens (bfloat16; head sizes that are multiples of 8 up to
-    128; pages of 64 positions).  tile_seq / tile_first describe the tiles of 64 new tokens."""
-    if hd % 8 != 0 or hd > 128 or page != 64:
-        raise Backend(f"attn_prefill: head size {hd} / page {page} not taken (multiples of 8 up to 128; page 64)")
+    128; pages of 64 positions).  tile_seq / tile_first describe the tiles of 64 new tokens.  ``vd``: size of a
+    value head (default: the key size); ``scale`` > 0 multiplies the scores instead of the division by sqrt(hd);
+    ``sink``: the softmax's denominator holds one more term exp(0)."""
+    vd = hd if vd is None else vd
+    if not attn_flash_fits(hd, vd, page):
+        raise Backend(f"attn_prefill: head sizes {hd} / {vd} / page {page} not taken (multiples of 8 up to 128; page 64)")
     _check(_fn("bf16", "esp_attn_prefill")(
         _ptr(q, torch.bfloat16, "q"), _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16),
         _ptr(out, torch.bfloat16), _ptr(tile_seq, torch.int32), _ptr(tile_first, torch.int32),
         _ptr(seq_start, torch.int32), _ptr(seq_past, torch.int32), _ptr(block_table, torch.int32),
-        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, int(window or 0),
-        _ptr(status, torch.int32), _stream()), "attn_prefill")
+        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, vd, float(scale), 1 if sink else 0,
+        int(window or 0), _ptr(status, torch.int32), _stream()), "attn_prefill")
 
 
 ATTN_TC05_TILE_ROWS = 128      # new tokens of a sequence to a tile of attn_prefill_tc05
@@ -821,3 +847,126 @@ def attn_latent_mma(qx, pool, out, tile_seq, tile_first, seq_start, seq_past, bl
         _ptr(block_table, torch.int32), block_table.shape[1], pool.shape[0], page, tile_seq.shape[0], n, heads,
         attn_latent_mma_heads(heads), key_dim, value_dim, int(window or 0), float(scale), int(n_splits), int(pages_per_split),
         _ptr(part_o, torch.float32), _ptr(part_ml, torch.float32), _ptr(status, torch.int32), _stream()), "attn_latent_mma")
+
+
+# ---------------------------------------------------------------------------
+# summed embeddings, norms around a sublayer, squared ReLU
+
+def embed_sum(table, bigram, freq, ids, tok_seq, tok_pos, seq_start, seq_slot, prev_state, x, status, buckets=0, mul_prev=0,
+              mul_cur=0, scale: float = 1.0):
+    """x[n] = scale * table[ids[n]] + bigram[hash(previous token, token)] + sinusoid(position).  ``bigram``
+    [buckets + 1, width] and ``freq`` (float32 [ceil(width / 2)]) may be None.  ``prev_state`` (int32 [slots]) holds
+    every sequence's last token + 1 (0: none yet); it is read for a run's first token and left at the run's last."""
+    n, width = x.shape
+    if bigram is not None and (bigram.dtype != table.dtype or bigram.shape != (buckets + 1, width)):
+        raise Backend("embed_sum: the bigram table must be [buckets + 1, width] in the token table's dtype")
+    if freq is not None and freq.shape[0] * 2 < width:
+        raise Backend("embed_sum: too few frequencies for the width")
+    _check(_fn("core", "esp_embed_sum")(
+        _ptr(table, FLOATS, "embedding table"), _ptr(bigram, FLOATS, "bigram table"), _is_bf16(table),
+        _ptr(freq, torch.float32, "freq"), _ptr(ids, torch.int32, "ids"), _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32),
+        _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(prev_state, torch.int32, "prev_state"),
+        _ptr(x, torch.float32, "x"), n, width, table.shape[0], int(buckets), int(mul_prev), int(mul_cur), float(scale),
+        _ptr(status, torch.int32), _stream()), "embed_sum")
+
+
+def norm_add_rmsnorm(x, y, gamma_y, eps_y, gamma, h, eps, rows=None, write_x=True, h32=None):
+    """x (+)= rmsnorm(y) * gamma_y, then h = rmsnorm(x) * gamma, in one launch; all float32 but h.  ``h`` None: the
+    add alone.  ``x`` None: h32 = rmsnorm(y) * gamma_y and nothing else."""
+    width = y.shape[1]
+    if x is None:
+        n_rows = h32.shape[0]
+    else:
+        n_rows = h.shape[0] if h is not None else x.shape[0]
+    _check(_fn("core", "esp_norm_add_rmsnorm")(
+        _ptr(x, torch.float32, "x"), _ptr(y, torch.float32, "y"), _ptr(gamma_y, torch.float32, "gamma_y"), float(eps_y),
+        _ptr(gamma, torch.float32, "gamma"), _ptr(rows, torch.int32, "rows"), _ptr(h, FLOATS, "h"),
+        _is_bf16(h) if h is not None else 0, _ptr(h32, torch.float32, "h32"), n_rows, width, float(eps),
+        1 if write_x else 0, _stream()), "norm_add_rmsnorm")
+
+
+def relu2(z, act, row_scale=None):
+    """act[m, :] = max(z[m, :] * row_scale[m], 0)^2; z float32 [M, W], act float32 or bfloat16."""
+    rows, width = act.shape
+    if z.shape[0] < rows or z.shape[1] != width:
+        raise Backend("relu2: shapes disagree")
+    _check(_fn("core", "esp_relu2")(_ptr(z, torch.float32, "z"), _ptr(row_scale, torch.float32, "row_scale"),
+                                    _ptr(act, FLOATS, "act"), _is_bf16(act), rows, width, _stream()), "relu2")
+
+
+def qknorm_kvwrite(qkv, bias, q_w, k_w, eps, temp_coef, temp_every, tok_seq, tok_pos, q_out, k_cache, v_cache, block_table,
+                   page, nh, nkv, hd, vd, write_kv, status):
+    """Bias, RMS norm per query and key head (weights q_w, k_w of hd numbers, None: no norm), the queries' factor
+    1 + temp_coef ln(floor((p + 1) / temp_every) + 1) (temp_every 0: none), and the write of keys [pages, nkv, page,
+    hd] and values [pages, nkv, page, vd] into the paged cache.  qkv float32 [N, nh*hd + nkv*hd + nkv*vd]."""
+    n = qkv.shape[0]
+    if qkv.shape[1] != (nh + nkv) * hd + nkv * vd:
+        raise Backend("qknorm_kvwrite: qkv width disagrees with the head counts")
+    _check(_fn("core", "esp_qknorm_kvwrite")(
+        _ptr(qkv, torch.float32, "qkv"), _ptr(bias, torch.float32, "bias"), _ptr(q_w, torch.float32), _ptr(k_w, torch.float32),
+        float(eps), float(temp_coef), int(temp_every), _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32),
+        _ptr(q_out, FLOATS, "q_out"), _ptr(k_cache, q_out.dtype), _ptr(v_cache, q_out.dtype), _is_bf16(q_out),
+        _ptr(block_table, torch.int32), block_table.shape[1], k_cache.shape[0], page, n, nh, nkv, hd, vd,
+        1 if write_kv else 0, _ptr(status, torch.int32), _stream()), "qknorm_kvwrite")
+
+
+# ---------------------------------------------------------------------------
+# matrix memory and gated diagonal recurrence (library ``mixers``)
+
+def matrix_memory_prepare(q, k, v, gi, gf, ld, bias_i, bias_f, cap, q_scale, m_state, seq_start, seq_slot, q_out, k_out,
+                          d_out, v_out, m_out, n_seqs, heads, key_dim, value_dim, value_cols):
+    """Gates of a matrix memory with exponential gating and what ``gated_scan(SCAN_LOWER_SIGMOID, ready=True)`` reads:
+    q, k, v, gi, gf are views into one float32 projection with row stride ``ld``; m_state float32 [slots, heads] (a
+    view with its slot stride); outputs float32: q_out, k_out, d_out [N, heads*key_dim], v_out [N, heads*value_cols]
+    (column value_dim is one, later ones zero), m_out [N, heads]."""
+    for t in (q, k, v, gi, gf):
+        if t.dtype != torch.float32 or t.stride(-1) != 1 or t.stride(0) != ld:
+            raise Backend("matrix_memory_prepare: the projections must be float32 views of rows with stride ld")
+    _check(_fn("mixers", "esp_matrix_memory_prepare")(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), gi.data_ptr(), gf.data_ptr(), int(ld), _ptr(bias_i, torch.float32),
+        _ptr(bias_f, torch.float32), float(cap), float(q_scale), m_state.data_ptr(), m_state.stride(0),
+        _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(q_out, torch.float32), _ptr(k_out, torch.float32),
+        _ptr(d_out, torch.float32), _ptr(v_out, torch.float32), _ptr(m_out, torch.float32), n_seqs, heads, key_dim,
+        value_dim, value_cols, _stream()), "matrix_memory_prepare")
+
+
+def matrix_memory_finish(o, m, w, gate, y, heads, value_dim, value_cols, eps, floor_eps):
+    """y[n, h, :] = unit-rms(o[n, h, :value_dim] / (max(|o[n, h, value_dim]|, exp(-m[n, h])) + floor_eps)) * w[h] *
+    sigmoid(gate[n, h, :]); o float32 [N, heads*value_cols], gate a float32 view [N, heads*value_dim] or None."""
+    n = o.shape[0]
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(-1) != 1):
+        raise Backend("matrix_memory_finish: the gate must be a float32 view with unit column stride")
+    _check(_fn("mixers", "esp_matrix_memory_finish")(
+        _ptr(o, torch.float32, "o"), _ptr(m, torch.float32, "m"), _ptr(w, torch.float32, "w"),
+        gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0, _ptr(y, FLOATS, "y"),
+        _is_bf16(y), n, heads, value_dim, value_cols, float(eps), float(floor_eps), _stream()), "matrix_memory_finish")
+
+
+CONV_MAX_TAPS = 16
+
+
+def conv_branches(proj, bias_y, bias_x, conv_w, conv_b, conv_state, tok_seq, seq_start, seq_slot, gate_out, u32, u_act,
+                  n_seqs, channels, taps):
+    """proj float32 [N, 2C] (gate branch, then input branch).  gate_out = gelu_tanh(proj_y + bias_y); u = causal
+    convolution of (proj_x + bias_x) over ``taps`` positions per channel (conv_w [C, taps], last column the token's
+    own; conv_state float32 [slots, (taps - 1) * C] (a view with its slot stride) holds a sequence's last taps - 1
+    inputs and is brought up to date); u32 float32, u_act in the activation dtype."""
+    if taps > CONV_MAX_TAPS:
+        raise Backend(f"conv_branches: {taps} taps are beyond the {CONV_MAX_TAPS} this kernel takes")
+    _check(_fn("mixers", "esp_conv_branches")(
+        _ptr(proj, torch.float32, "proj"), _ptr(bias_y, torch.float32), _ptr(bias_x, torch.float32),
+        _ptr(conv_w, torch.float32), _ptr(conv_b, torch.float32), conv_state.data_ptr(), conv_state.stride(0),
+        _ptr(tok_seq, torch.int32), _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32),
+        _ptr(gate_out, torch.float32), _ptr(u32, torch.float32), _ptr(u_act, FLOATS), _is_bf16(u_act), proj.shape[0],
+        n_seqs, channels, taps, _stream()), "conv_branches")
+
+
+def diag_scan(gates, bias_r, bias_i, lam, decay_scale, u, gate, state, seq_start, seq_slot, out, n_seqs, channels, blocks):
+    """S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t, a_t = exp(-decay_scale sigmoid(raw_r + bias_r) softplus(lam)),
+    i_t = sigmoid(raw_i + bias_i); out = S_t * gate.  gates float32 [N, blocks, 2, C / blocks]; state float32 [slots, C]
+    (a view with its slot stride)."""
+    _check(_fn("mixers", "esp_diag_scan")(
+        _ptr(gates, torch.float32, "gates"), _ptr(bias_r, torch.float32), _ptr(bias_i, torch.float32),
+        _ptr(lam, torch.float32), float(decay_scale), _ptr(u, torch.float32), _ptr(gate, torch.float32), state.data_ptr(),
+        state.stride(0), _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(out, FLOATS), _is_bf16(out),
+        n_seqs, channels, blocks, _stream()), "diag_scan")

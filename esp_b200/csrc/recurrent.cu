@@ -367,6 +367,213 @@ __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const floa
         y[((size_t)n * H + h) * V + i] = from_f32<T>(r);
     }
 }
+
+// ---------------------------------------------------------------------------------------------- matrix memory
+// The gates of a matrix memory with exponential gating, ahead of esp_gated_scan(mode 1, ready): per head and token
+//     i = cap tanh((raw_i + b_i) / cap),  f = logsigmoid(cap tanh((raw_f + b_f) / cap)),
+//     m_t = max(f + m_(t-1), i),  keep = exp(f + m_(t-1) - m_t),  take = exp(i - m_t)
+// and from them what the recurrence reads: q_out = q * q_scale, k_out = take * k, d_out = keep on every key channel,
+// v_out = [v, 1, 0 ...] (V1 >= V + 1 columns a head: column V accumulates the normaliser n_t = keep n_(t-1) + take k_t as
+// one more value column of the same recurrence; further columns are zero and only align the rows), m_out = m_t.  m_(t-1) of a run's first token is the sequence's state
+// (m_state[slot * state_stride + h], zero in a fresh slot), which the run's last m_t replaces.  A block owns
+// (sequence, head); the gates of 128 tokens are made in parallel, one thread then walks the chain of maxima (an add
+// and a max per token, in token order, so cutting a sequence into steps changes no bit), and all write the rows.
+constexpr int MM_CHUNK = 128;
+
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+__global__ void __launch_bounds__(MM_CHUNK)
+matrix_memory_prepare_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                             const float* __restrict__ gi, const float* __restrict__ gf, long long ld,
+                             const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap, float q_scale,
+                             float* __restrict__ m_state, long long state_stride, const int* __restrict__ seq_start,
+                             const int* __restrict__ seq_slot, float* __restrict__ q_out, float* __restrict__ k_out,
+                             float* __restrict__ d_out, float* __restrict__ v_out, float* __restrict__ m_out, int H, int K,
+                             int V, int V1) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float s_i[MM_CHUNK], s_f[MM_CHUNK], s_keep[MM_CHUNK], s_take[MM_CHUNK];
+    __shared__ float s_m;
+    const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int row0 = seq_start[b], row1 = seq_start[b + 1];
+    if (row1 <= row0) return;
+    float* mp = m_state + (size_t)seq_slot[b] * state_stride + h;
+    if (tid == 0) s_m = *mp;
+    const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
+    for (int r0 = row0; r0 < row1; r0 += MM_CHUNK) {
+        const int count = min(MM_CHUNK, row1 - r0);
+        __syncthreads();
+        if (tid < count) {
+            const size_t r = (size_t)(r0 + tid);
+            s_i[tid] = cap * tanhf((gi[r * ld + h] + bi) / cap);
+            s_f[tid] = log_sigmoid(cap * tanhf((gf[r * ld + h] + bf) / cap));
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float m = s_m;
+            for (int t = 0; t < count; t++) {
+                const float carried = __fadd_rn(s_f[t], m);
+                const float m_new = fmaxf(carried, s_i[t]);
+                s_keep[t] = carried;                 // turned into exp(carried - m_new) below, in parallel
+                s_take[t] = m_new;
+                m = m_new;
+            }
+            s_m = m;
+        }
+        __syncthreads();
+        if (tid < count) {
+            const float m_new = s_take[tid];
+            m_out[(size_t)(r0 + tid) * H + h] = m_new;
+            s_keep[tid] = expf(s_keep[tid] - m_new);
+            s_take[tid] = expf(s_i[tid] - m_new);
+        }
+        __syncthreads();
+        for (int idx = tid; idx < count * K; idx += MM_CHUNK) {
+            const int t = idx / K, c = idx - t * K;
+            const size_t r = (size_t)(r0 + t);
+            const size_t o = (r * H + h) * K + c;
+            q_out[o] = q[r * ld + h * K + c] * q_scale;
+            k_out[o] = k[r * ld + h * K + c] * s_take[t];
+            d_out[o] = s_keep[t];
+        }
+        for (int idx = tid; idx < count * V1; idx += MM_CHUNK) {
+            const int t = idx / V1, c = idx - t * V1;
+            const size_t r = (size_t)(r0 + t);
+            v_out[(r * H + h) * V1 + c] = c < V ? v[r * ld + h * V + c] : (c == V ? 1.0f : 0.f);
+        }
+    }
+    __syncthreads();
+    if (tid == 0) *mp = s_m;
+}
+
+// What follows the recurrence (o has V1 columns a head): o[n, h, :V] / (max(|o[n, h, V]|, exp(-m[n, h])) + floor_eps), each head scaled to unit
+// root mean square (eps inside the root), times a weight per channel, times sigmoid(gate).  One warp per (row, head).
+template <typename T>
+__global__ void matrix_memory_finish_kernel(const float* __restrict__ o, const float* __restrict__ m,
+                                            const float* __restrict__ w, const float* __restrict__ gate, long long ldgate,
+                                            T* __restrict__ y, int n_rows, int H, int V, int V1, float eps,
+                                            float floor_eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= n_rows * H) return;
+    const int n = warp / H, h = warp - n * H;
+    const float* src = o + ((size_t)n * H + h) * V1;
+    const float den = fmaxf(fabsf(src[V]), expf(-m[(size_t)n * H + h])) + floor_eps;
+    float ss = 0.f;
+    for (int i = lane; i < V; i += 32) {
+        const float val = src[i] / den;
+        ss = fmaf(val, val, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+    for (int i = lane; i < V; i += 32) {
+        float r = src[i] / den * inv * w[h * V + i];
+        if (gate) r *= 1.0f / (1.0f + expf(-gate[(size_t)n * ldgate + h * V + i]));
+        y[((size_t)n * H + h) * V + i] = from_f32<T>(r);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- gated diagonal recurrence
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// The two branches ahead of the recurrence.  proj: [rows, 2C] float, the gate branch's projection in columns [0, C),
+// the input branch's in [C, 2C).  gate_out = gelu_tanh(proj_y + bias_y);  u = conv_b + sum_j conv_w[c, j] * xin[t - (taps
+// - 1) + j, c] with xin = proj_x + bias_x, the last column being the token's own; inputs ahead of a run's first token
+// come from the sequence's state (conv_state[slot]: [taps - 1, C], oldest first; zeros in a fresh slot).  u goes out in
+// 32-bit (the recurrence reads it) and in the activation dtype (the gates' projections read it).
+template <typename T>
+__global__ void conv_branches_kernel(const float* __restrict__ proj, const float* __restrict__ bias_y,
+                                     const float* __restrict__ bias_x, const float* __restrict__ conv_w,
+                                     const float* __restrict__ conv_b, const float* __restrict__ conv_state,
+                                     long long state_stride, const int* __restrict__ tok_seq,
+                                     const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                                     float* __restrict__ gate_out, float* __restrict__ u32, T* __restrict__ u_act, int C,
+                                     int taps) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int seq = tok_seq[n];
+    const int in_run = n - seq_start[seq];
+    const float* st = conv_state + (size_t)seq_slot[seq] * state_stride;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        gate_out[(size_t)n * C + c] = gelu_tanh_f(proj[(size_t)n * 2 * C + c] + (bias_y ? bias_y[c] : 0.f));
+        float u = conv_b ? conv_b[c] : 0.f;
+        const float bx = bias_x ? bias_x[c] : 0.f;
+        for (int j = 0; j < taps; j++) {
+            const int back = taps - 1 - j;
+            float xin;
+            if (in_run - back >= 0) xin = proj[(size_t)(n - back) * 2 * C + C + c] + bx;
+            else xin = st[(size_t)(taps - 1 + in_run - back) * C + c];
+            u = fmaf(conv_w[(size_t)c * taps + j], xin, u);
+        }
+        u32[(size_t)n * C + c] = u;
+        u_act[(size_t)n * C + c] = from_f32<T>(u);
+    }
+}
+
+// conv_state[slot] <- the last taps - 1 inputs of the sequence after this step (a thread owns a channel: it reads what
+// it needs of the old state before it writes).
+constexpr int CONV_MAX_TAPS = 16;
+__global__ void conv_state_keep_kernel(const float* __restrict__ proj, const float* __restrict__ bias_x,
+                                       float* __restrict__ conv_state, long long state_stride,
+                                       const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int C, int taps) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int row0 = seq_start[b], run = seq_start[b + 1] - row0;
+    if (run <= 0) return;
+    float* st = conv_state + (size_t)seq_slot[b] * state_stride;
+    const int keep = taps - 1;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        float next[CONV_MAX_TAPS];
+        for (int j = 0; j < keep; j++) {
+            const int e = run + j;                   // index in (old state, then the run's inputs)
+            next[j] = e < keep ? st[(size_t)e * C + c]
+                               : proj[(size_t)(row0 + e - keep) * 2 * C + C + c] + (bias_x ? bias_x[c] : 0.f);
+        }
+        for (int j = 0; j < keep; j++) st[(size_t)j * C + c] = next[j];
+    }
+}
+
+// S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t with a_t = exp(-decay_scale r_t softplus(lam)), r_t = sigmoid(raw_r + b_r),
+// i_t = sigmoid(raw_i + b_i); out = S_t * gate.  gates: [rows, blocks, 2, C / blocks] float (a block's r then its i, as the
+// block-diagonal projection leaves them).  S lives in state[slot * state_stride + c], 32-bit.  A thread owns (sequence,
+// channel) and walks the run's tokens in order; 1 - a^2 is taken as -expm1(2 ln a).
+template <typename T>
+__global__ void __launch_bounds__(128)
+diag_scan_kernel(const float* __restrict__ gates, const float* __restrict__ bias_r, const float* __restrict__ bias_i,
+                 const float* __restrict__ lam, float decay_scale, const float* __restrict__ u, const float* __restrict__ gate,
+                 float* __restrict__ state, long long state_stride, const int* __restrict__ seq_start,
+                 const int* __restrict__ seq_slot, T* __restrict__ out, int C, int cb) {
+    pdl_trigger();
+    pdl_wait();
+    const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int row0 = seq_start[b], row1 = seq_start[b + 1];
+    if (row1 <= row0) return;
+    const int blk = c / cb, j = c - blk * cb;
+    const size_t goff = (size_t)blk * 2 * cb + j;
+    const float br = bias_r ? bias_r[c] : 0.f, bi = bias_i ? bias_i[c] : 0.f;
+    const float l = lam[c];
+    const float rate = decay_scale * (l > 20.f ? l : log1pf(expf(l)));
+    float* sp = state + (size_t)seq_slot[b] * state_stride + c;
+    float S = *sp;
+#pragma unroll 4
+    for (int r = row0; r < row1; r++) {
+        const float* g = gates + (size_t)r * 2 * C + goff;
+        const float rr = 1.0f / (1.0f + expf(-(g[0] + br)));
+        const float ii = 1.0f / (1.0f + expf(-(g[cb] + bi)));
+        const float log_a = -rate * rr;
+        const float a = expf(log_a);
+        const float in = sqrtf(-expm1f(2.0f * log_a)) * (ii * u[(size_t)r * C + c]);
+        S = fmaf(a, S, in);
+        out[(size_t)r * C + c] = from_f32<T>(S * gate[(size_t)r * C + c]);
+    }
+    *sp = S;
+}
 }  // namespace
 
 ESP_API int esp_token_shift_mix(const void* h, int is_bf16, const float* prev_state, long long state_stride,
@@ -462,5 +669,71 @@ ESP_API int esp_head_rmsnorm_gate(const float* o, const float* w, int w_head_str
     else
         esp_launch_pdl(ESP_PDL_SMALL, head_rmsnorm_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, o, w, w_head_stride,
                        gate, ldgate, (float*)y, n_rows, H, V, eps);
+    return esp_launch_status();
+}
+
+ESP_API int esp_matrix_memory_prepare(const float* q, const float* k, const float* v, const float* gi, const float* gf,
+                                      long long ld, const float* bias_i, const float* bias_f, float cap, float q_scale,
+                                      float* m_state, long long state_stride, const int* seq_start, const int* seq_slot,
+                                      float* q_out, float* k_out, float* d_out, float* v_out, float* m_out, int n_seqs, int H,
+                                      int K, int V, int V1, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (H <= 0 || H > 65535 || K <= 0 || V <= 0 || V1 <= V || !(cap > 0.f)) return (int)cudaErrorInvalidValue;
+    esp_launch_pdl(ESP_PDL_SMALL, matrix_memory_prepare_kernel, dim3(n_seqs, H), dim3(MM_CHUNK), 0, stream, q, k, v, gi, gf, ld,
+                   bias_i, bias_f, cap, q_scale, m_state, state_stride, seq_start, seq_slot, q_out, k_out, d_out, v_out, m_out,
+                   H, K, V, V1);
+    return esp_launch_status();
+}
+
+ESP_API int esp_matrix_memory_finish(const float* o, const float* m, const float* w, const float* gate, long long ldgate,
+                                     void* y, int y_is_bf16, int n_rows, int H, int V, int V1, float eps, float floor_eps,
+                                     cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const long long warps = (long long)n_rows * H;
+    const int blocks = (int)((warps + 7) / 8);
+    if (y_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, matrix_memory_finish_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, o, m, w, gate,
+                       ldgate, (bf16*)y, n_rows, H, V, V1, eps, floor_eps);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, matrix_memory_finish_kernel<float>, dim3(blocks), dim3(256), 0, stream, o, m, w, gate,
+                       ldgate, (float*)y, n_rows, H, V, V1, eps, floor_eps);
+    return esp_launch_status();
+}
+
+// Both branches of a step's rows, then the sequences' convolution states.
+ESP_API int esp_conv_branches(const float* proj, const float* bias_y, const float* bias_x, const float* conv_w,
+                              const float* conv_b, float* conv_state, long long state_stride, const int* tok_seq,
+                              const int* seq_start, const int* seq_slot, float* gate_out, float* u32, void* u_act,
+                              int act_is_bf16, int n_rows, int n_seqs, int C, int taps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (taps < 1 || taps > CONV_MAX_TAPS || C <= 0) return (int)cudaErrorInvalidValue;
+    const int threads = C >= 1024 ? 256 : 128;
+    if (act_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, conv_branches_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, proj, bias_y, bias_x,
+                       conv_w, conv_b, (const float*)conv_state, state_stride, tok_seq, seq_start, seq_slot, gate_out, u32,
+                       (bf16*)u_act, C, taps);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, conv_branches_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, proj, bias_y, bias_x,
+                       conv_w, conv_b, (const float*)conv_state, state_stride, tok_seq, seq_start, seq_slot, gate_out, u32,
+                       (float*)u_act, C, taps);
+    if (taps > 1)
+        esp_launch_pdl(ESP_PDL_SMALL, conv_state_keep_kernel, dim3(n_seqs, (C + 127) / 128), dim3(128), 0, stream, proj, bias_x,
+                       conv_state, state_stride, seq_start, seq_slot, C, taps);
+    return esp_launch_status();
+}
+
+ESP_API int esp_diag_scan(const float* gates, const float* bias_r, const float* bias_i, const float* lam, float decay_scale,
+                          const float* u, const float* gate, float* state, long long state_stride, const int* seq_start,
+                          const int* seq_slot, void* out, int out_is_bf16, int n_seqs, int C, int blocks,
+                          cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (C <= 0 || blocks <= 0 || C % blocks != 0) return (int)cudaErrorInvalidValue;
+    dim3 grid(n_seqs, (C + 127) / 128);
+    if (out_is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, diag_scan_kernel<bf16>, grid, dim3(128), 0, stream, gates, bias_r, bias_i, lam, decay_scale,
+                       u, gate, state, state_stride, seq_start, seq_slot, (bf16*)out, C, C / blocks);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, diag_scan_kernel<float>, grid, dim3(128), 0, stream, gates, bias_r, bias_i, lam, decay_scale,
+                       u, gate, state, state_stride, seq_start, seq_slot, (float*)out, C, C / blocks);
     return esp_launch_status();
 }

@@ -173,3 +173,89 @@ ESP_API int esp_rope_kvwrite(const float* qkv, const float* bias, const int* tok
                                                                 write_kv, heads_per_block, status);
     return esp_launch_status();
 }
+
+// ---------------------------------------------------------------- queries and keys with a norm per head, no rotation
+// qkv: [n_tokens, nh*hd + nkv*hd + nkv*vd] float; ``bias`` (same width, may be null) is added first.  Every query
+// and key head is divided by its root mean square (eps inside the root) and multiplied by a weight vector of hd
+// numbers that all heads share (q_w, k_w; null: no norm for that side).  Queries are then multiplied by
+// 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1), p the token's position (temp_every 0: no such factor).
+// Keys [pages, nkv, PAGE, hd] and values [pages, nkv, PAGE, vd] go to the token's place in the paged cache.
+// One warp per head; everything in 32-bit.
+template <typename T>
+__global__ void qknorm_kvwrite_kernel(const float* __restrict__ qkv, const float* __restrict__ bias,
+                                      const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                      float temp_coef, int temp_every, const int* __restrict__ tok_seq,
+                                      const int* __restrict__ tok_pos, T* __restrict__ q_out, T* __restrict__ k_cache,
+                                      T* __restrict__ v_cache, const int* __restrict__ block_table, int table_stride,
+                                      int n_pages, int page, int nh, int nkv, int hd, int vd, int write_kv,
+                                      int* __restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    const int pos = tok_pos[n], seq = tok_seq[n];
+    const size_t width = (size_t)(nh + nkv) * hd + (size_t)nkv * vd;
+    const float* src = qkv + (size_t)n * width;
+    int page_id = -1;
+    if (write_kv) {
+        page_id = block_table[(size_t)seq * table_stride + pos / page];
+        if (page_id < 0 || page_id >= n_pages) {
+            if (threadIdx.x == 0) atomicOr(status, ESP_STATUS_BAD_INDEX);
+            page_id = -1;
+        }
+    }
+    const int in_page = pos % page;
+    float q_factor = 1.0f;
+    if (temp_every > 0) q_factor = 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f);
+    for (int head = warp; head < nh + 2 * nkv; head += nwarp) {
+        if (head < nh + nkv) {
+            const float* x = src + (size_t)head * hd;
+            const float* b = bias ? bias + (size_t)head * hd : nullptr;
+            const float* w = head < nh ? q_w : k_w;
+            float ss = 0.f;
+            for (int i = lane; i < hd; i += 32) {
+                const float v = x[i] + (b ? b[i] : 0.f);
+                ss = fmaf(v, v, ss);
+            }
+            ss = warp_sum(ss);
+            const float inv = w ? 1.0f / sqrtf(ss / (float)hd + eps) : 1.0f;
+            T* dst;
+            if (head < nh) dst = q_out + ((size_t)n * nh + head) * hd;
+            else if (page_id >= 0) dst = k_cache + (((size_t)page_id * nkv + (head - nh)) * page + in_page) * hd;
+            else continue;
+            const float f = head < nh ? q_factor : 1.0f;
+            for (int i = lane; i < hd; i += 32) {
+                float v = x[i] + (b ? b[i] : 0.f);
+                if (w) v = v * inv * w[i];
+                dst[i] = from_f32<T>(v * f);
+            }
+        } else if (page_id >= 0) {
+            const int vh = head - nh - nkv;
+            const size_t off = (size_t)(nh + nkv) * hd + (size_t)vh * vd;
+            const float* x = src + off;
+            const float* b = bias ? bias + off : nullptr;
+            T* dst = v_cache + (((size_t)page_id * nkv + vh) * page + in_page) * vd;
+            for (int i = lane; i < vd; i += 32) dst[i] = from_f32<T>(x[i] + (b ? b[i] : 0.f));
+        }
+    }
+}
+
+ESP_API int esp_qknorm_kvwrite(const float* qkv, const float* bias, const float* q_w, const float* k_w, float eps,
+                               float temp_coef, int temp_every, const int* tok_seq, const int* tok_pos, void* q_out,
+                               void* k_cache, void* v_cache, int is_bf16, const int* block_table, int table_stride,
+                               int n_pages, int page, int n_tokens, int nh, int nkv, int hd, int vd, int write_kv,
+                               int* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd <= 0 || vd <= 0 || nkv <= 0 || nh <= 0 || page <= 0) return (int)cudaErrorInvalidValue;
+    const int heads = nh + 2 * nkv;
+    const int threads = heads >= 8 ? 256 : 32 * heads;
+    if (is_bf16)
+        esp_launch_pdl(ESP_PDL_SMALL, qknorm_kvwrite_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, stream, qkv, bias, q_w, k_w,
+                       eps, temp_coef, temp_every, tok_seq, tok_pos, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, block_table,
+                       table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
+    else
+        esp_launch_pdl(ESP_PDL_SMALL, qknorm_kvwrite_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, qkv, bias, q_w,
+                       k_w, eps, temp_coef, temp_every, tok_seq, tok_pos, (float*)q_out, (float*)k_cache, (float*)v_cache,
+                       block_table, table_stride, n_pages, page, nh, nkv, hd, vd, write_kv, status);
+    return esp_launch_status();
+}

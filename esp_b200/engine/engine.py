@@ -89,7 +89,7 @@ class Engine:
                 max_slots = max(1, min(n_pages, 4096))
             self.max_slots = max_slots
             self.cache = Cache(self.model.cache_requests(), max_tokens, max_slots, self.plan.max_positions,
-                               self.dtype, self.rt.device)
+                               self.dtype, self.rt.device, model_states=self.model.model_states())
         parts = self.model.all_parts()
         # a decode step is replayed from a captured graph only if every part says that it may be
         self._parts_graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
@@ -136,7 +136,7 @@ class Engine:
         per_token, per_slot = 0, 0
         for layout, state, cache_of in self.model.cache_requests():
             if layout is not None and cache_of is None:
-                per_token += (2 if layout.values else 1) * layout.num_kv_heads * layout.head_dim * el[self.dtype]
+                per_token += layout.row_elements * el[self.dtype]
             if state is not None:
                 per_slot += int(np.prod(state.shape)) * el.get(state.dtype, 4)
         # the mixers' states of fixed size: one row per slot
@@ -364,7 +364,7 @@ class Engine:
         c["tokens"] += sum(news)
         el = torch.empty((), dtype=self.dtype).element_size()
         for layout, members in zip(self.cache.layouts, self.cache.members):
-            per_key = (2 if layout.values else 1) * len(members) * layout.num_kv_heads * layout.head_dim * el
+            per_key = len(members) * layout.row_elements * el
             seen = 0
             for p, t in zip(pasts, news):
                 # the keys the sequence's last new token sees: every kernel streams a sequence's visible keys once

@@ -22,6 +22,7 @@ class DecoderModel(Part):
         self.rt = rt
         self.blocks = [build("block", spec, rt) for spec in plan.blocks]
         self.final_norm = build("norm", plan.final_norm, rt)
+        self.embedding = build("embedding", plan.embedding, rt)      # None: the token's row alone
         self.embed = None
         self.head = None
         for i, e in enumerate(plan.schedule):
@@ -29,7 +30,7 @@ class DecoderModel(Part):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the plan has {len(self.blocks)}")
 
     def children(self):
-        return [*self.blocks, self.final_norm]
+        return [p for p in (self.embedding, *self.blocks, self.final_norm) if p is not None]
 
     # -- parameters ---------------------------------------------------------------
     def param_specs(self):
@@ -46,6 +47,8 @@ class DecoderModel(Part):
         p = self.plan
         self.embed = torch.empty((p.vocab, p.hidden), dtype=rt.matrix_dtype([stored[p.embed_weight]]), device=rt.device)
         views = {p.embed_weight: self.embed}
+        if self.embedding is not None:
+            views.update(self.embedding.allocate_with(stored, rt, self.embed.dtype))
         head_name = p.head_weight or p.tied_head_name
         if head_name is not None and head_name in stored:
             self.head = torch.empty((p.vocab, p.hidden), dtype=rt.matrix_dtype([stored[head_name]]), device=rt.device)
@@ -67,13 +70,21 @@ class DecoderModel(Part):
             out.append((layout, state, e.cache_of))
         return out
 
+    def model_states(self) -> dict:
+        """name -> StateSpec of per-sequence state that belongs to no layer."""
+        spec = self.embedding.state_spec() if self.embedding is not None else None
+        return {"embedding": spec} if spec is not None else {}
+
     # -- running ------------------------------------------------------------------
     def forward(self, ctx, cache):
         """Logits [R, vocab] float32 at ctx.want_rows (R may be 0)."""
         rt, p = self.rt, self.plan
         n = ctx.n_tokens
         x = rt.ws.get("residual", (n, p.hidden), torch.float32)
-        ops.embed_gather(self.embed, ctx.tok_ids, x, rt.status, scale=p.embed_scale)
+        if self.embedding is not None:
+            self.embedding.forward(self.embed, ctx, x, cache.named_state.get("embedding"), scale=p.embed_scale)
+        else:
+            ops.embed_gather(self.embed, ctx.tok_ids, x, rt.status, scale=p.embed_scale)
         pending = None
         for idx, entry in enumerate(p.schedule):
             pending = self.blocks[entry.layer].forward(x, pending, ctx, cache.layers[idx])

@@ -178,4 +178,113 @@ class Attention(Part):
                           s.num_kv_heads, s.head_dim, s.window, rt.status)
 
 
+class NormedAttention(Part):
+    """Causal softmax attention without rotation over the paged cache: packed q/k/v projection (+bias), an RMS norm
+    per query and key head (one weight vector for all heads of a side), a factor on the queries that grows with the
+    logarithm of the position in steps, keys and values of different sizes, scores times the spec's scale, and
+    (``sink``) one more term exp(0) in the softmax's denominator.  Keys are cached after their norm.  Query head i
+    reads key/value head i // (num_heads / num_kv_heads)."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        s = spec
+        if s.key_dim > 256 or s.value_dim > 256:
+            raise Unsupported("dim", f"{s.key_dim} / {s.value_dim}; the attention kernels take head sizes up to 256")
+        if s.num_heads % s.num_kv_heads != 0:
+            raise Unsupported("kv_heads", f"{s.num_kv_heads} does not divide {s.num_heads} heads")
+        self.q_width = s.num_heads * s.key_dim
+        self.k_width = s.num_kv_heads * s.key_dim
+        self.v_width = s.num_kv_heads * s.value_dim
+        self.o_width = s.num_heads * s.value_dim
+        self.qkv_width = self.q_width + self.k_width + self.v_width
+        self.w_qkv = self.b_qkv = self.w_o = self.q_norm = self.k_norm = None
+
+    def _n(self, which, bias=False):
+        n = self.spec.names
+        return self.spec.prefix + getattr(n, which) + (n.bias if bias else "")
+
+    def param_specs(self):
+        s = self.spec
+        specs = [ParamSpec(self._n("q"), (self.q_width, s.hidden), "matrix"),
+                 ParamSpec(self._n("k"), (self.k_width, s.hidden), "matrix"),
+                 ParamSpec(self._n("v"), (self.v_width, s.hidden), "matrix"),
+                 ParamSpec(self._n("o"), (s.hidden, self.o_width), "matrix"),
+                 ParamSpec(self._n("q_norm"), (s.key_dim,), "norm_scale"),
+                 ParamSpec(self._n("k_norm"), (s.key_dim,), "norm_scale")]
+        if s.qkv_bias:
+            specs += [ParamSpec(self._n("q", True), (self.q_width,), "bias"),
+                      ParamSpec(self._n("k", True), (self.k_width,), "bias"),
+                      ParamSpec(self._n("v", True), (self.v_width,), "bias")]
+        return specs
+
+    def allocate(self, stored, rt):
+        s, dev = self.spec, rt.device
+        names = [self._n("q"), self._n("k"), self._n("v")]
+        self.w_qkv = torch.empty((self.qkv_width, s.hidden), dtype=rt.matrix_dtype([stored[n] for n in names]), device=dev)
+        self.w_o = torch.empty((s.hidden, self.o_width), dtype=rt.matrix_dtype([stored[self._n("o")]]), device=dev)
+        self.q_norm = torch.empty(s.key_dim, dtype=torch.float32, device=dev)
+        self.k_norm = torch.empty(s.key_dim, dtype=torch.float32, device=dev)
+        a, b = self.q_width, self.q_width + self.k_width
+        views = {names[0]: self.w_qkv[:a], names[1]: self.w_qkv[a:b], names[2]: self.w_qkv[b:], self._n("o"): self.w_o,
+                 self._n("q_norm"): self.q_norm, self._n("k_norm"): self.k_norm}
+        if s.qkv_bias:
+            self.b_qkv = torch.empty(self.qkv_width, dtype=torch.float32, device=dev)
+            views.update({self._n("q", True): self.b_qkv[:a], self._n("k", True): self.b_qkv[a:b],
+                          self._n("v", True): self.b_qkv[b:]})
+        return views
+
+    def kv_layout(self):
+        s = self.spec
+        return KvLayout(s.num_kv_heads, s.key_dim, s.window, value_dim=s.value_dim if s.value_dim != s.key_dim else None)
+
+    def state_spec(self):
+        return None
+
+    # -- which kernel a step of n token rows gets, and the index lists it needs ----------
+    def kernel_for(self, n: int, page: int = PAGE) -> str:
+        s = self.spec
+        if self.rt.dtype == torch.bfloat16 and page == PAGE and ops.attn_flash_fits(s.key_dim, s.value_dim):
+            return "flash"
+        return "plain"
+
+    def step_arrays_key(self):
+        return ("attention_qknorm", self.rt.dtype, ops.attn_flash_fits(self.spec.key_dim, self.spec.value_dim))
+
+    def step_arrays(self, step):
+        """Tiles of 64 new tokens for the tensor-core kernel: (sequence, first new token) per tile."""
+        if self.kernel_for(step.n_tokens) != "flash":
+            return {}
+        tiles = [(i, f) for i, t in enumerate(step.news) for f in range(0, t, 64)]
+        return {"attention.tiles64.seq": np.asarray([t[0] for t in tiles], dtype=np.int32),
+                "attention.tiles64.first": np.asarray([t[1] for t in tiles], dtype=np.int32)}
+
+    def forward(self, h, ctx, layer):
+        s, rt = self.spec, self.rt
+        n = h.shape[0]
+        table = ctx.block_tables[layer.group]
+        qkv = rt.ws.get("attn_qkv", (n, self.qkv_width), torch.float32)
+        linear(rt, h, self.w_qkv, qkv)
+        q = rt.ws.get("attn_q", (n, self.q_width), rt.dtype)
+        temp = s.q_temp
+        ops.qknorm_kvwrite(qkv, self.b_qkv, self.q_norm, self.k_norm, s.eps, temp.coef if temp else 0.0,
+                           temp.every if temp else 0, ctx.tok_seq, ctx.tok_pos, q, layer.k, layer.v, table, layer.page,
+                           s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim, layer.writes, rt.status)
+        o = rt.ws.get("attn_o", (n, self.o_width), rt.dtype)
+        kind = self.kernel_for(n, layer.page)
+        tile_seq, tile_first = ctx.arrays.get("attention.tiles64.seq"), ctx.arrays.get("attention.tiles64.first")
+        if kind == "flash" and tile_seq is not None:
+            ops.attn_prefill(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past, table, layer.page,
+                             s.num_heads, s.num_kv_heads, s.key_dim, s.window, rt.status, vd=s.value_dim, scale=s.scale,
+                             sink=s.sink)
+        else:
+            ops.attn_simt(q, layer.k, layer.v, o, ctx.tok_seq, ctx.tok_pos, table, layer.page, s.num_heads, s.num_kv_heads,
+                          s.key_dim, s.window, rt.status, vd=s.value_dim, scale=s.scale, sink=s.sink)
+        y = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
+        linear(rt, o, self.w_o, y)
+        return y
+
+
 register("mixer", "attention", Attention)
+register("mixer", "attention_qknorm", NormedAttention)

@@ -19,6 +19,8 @@ Interfaces (all tensors live on the GPU; N = tokens of the step, H = width):
              ``project_rotate_store(h, w_qkv, bias, ctx, q_out, layer, nh, nkv, hd, status) -> bool`` does the
              packed projection as well, in one kernel, where the part has one for the sizes at hand.
 * block:     ``forward(x, pending, ctx, layer) -> pending``: runs its parts in its arrangement.
+* embedding: ``forward(table, ctx, x, state, scale)``: fills the residual stream from the token table and whatever
+             else the part adds; ``state_spec()`` says what it keeps per sequence (handed back as ``state``).
 
 Per-step index lists.  A part that needs lists of its own on the device (tiles
 of new tokens for an attention kernel, chunk boundaries for a scan) returns them
@@ -124,7 +126,7 @@ def walk(part: Part):
 # ---------------------------------------------------------------------------
 # registries: spec.kind -> builder(spec, rt) -> part
 # ---------------------------------------------------------------------------
-_REGISTRIES: dict = {"mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}}
+_REGISTRIES: dict = {"mixer": {}, "ffn": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}}
 
 
 def register(family: str, kind: str, builder: Callable) -> None:

@@ -5,6 +5,7 @@ import torch
 
 from ..csrc import ops
 from .base import ParamSpec, Part, build, plain_delta, register
+from .norm import DeferredPostNorm
 
 
 class PreNormResidualBlock(Part):
@@ -111,5 +112,45 @@ class ScaledDepthMixBlock(Part):
             ctx.aux["residual_trace"].append(x.clone())
 
 
+class SandwichBlock(Part):
+    """x += post1(mixer(pre1(x))); x += post2(ffn(pre2(x))): a norm before and a norm after every sublayer.  A
+    sublayer's result travels as a ``DeferredPostNorm`` until the next norm that reads x (this block's, the next
+    block's or the model's last) normalises it, adds it and normalises x, all in one launch."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.mixer_norm = build("norm", spec.mixer_norm, rt)
+        self.mixer_post = build("norm", spec.mixer_post_norm, rt)
+        self.mixer = build("mixer", spec.mixer, rt)
+        self.ffn_norm = build("norm", spec.ffn_norm, rt)
+        self.ffn_post = build("norm", spec.ffn_post_norm, rt)
+        self.ffn = build("ffn", spec.ffn, rt)
+
+    def children(self):
+        return [p for p in (self.mixer_norm, self.mixer, self.mixer_post, self.ffn_norm, self.ffn, self.ffn_post)
+                if p is not None]
+
+    def forward(self, x, pending, ctx, layer):
+        rt = self.rt
+        h = rt.ws.get("block_h", tuple(x.shape), rt.dtype)
+        self.mixer_norm.forward(x, plain_delta(self.mixer_norm, pending), h)
+        pending = DeferredPostNorm(rt, self.mixer.forward(h, ctx, layer), self.mixer_post)
+        if self.ffn is not None:
+            h32 = None
+            if rt.dtype != torch.float32 and getattr(self.ffn, "wants_f32_input", False):
+                h32 = rt.ws.get("block_h32", tuple(x.shape), torch.float32)
+            self.ffn_norm.forward(x, plain_delta(self.ffn_norm, pending), h, h32=h32)
+            pending = DeferredPostNorm(rt, plain_delta(None, self.ffn.forward(h, ctx, h32=h32)), self.ffn_post)
+        if "residual_trace" in ctx.aux:
+            # debugging aid (see ScaledDepthMixBlock._trace): the add is done here so that x is the layer's result
+            pending.add_to(x)
+            ctx.aux["residual_trace"].append(x.clone())
+            return None
+        return pending
+
+
 register("block", "prenorm_residual", PreNormResidualBlock)
+register("block", "sandwich_residual", SandwichBlock)
 register("block", "prenorm_scaled_depthmix", ScaledDepthMixBlock)

@@ -5,6 +5,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import ops
+from ..errors import Unsupported
 from .base import ParamSpec, Part, register
 from .linear import grouped_linear, grouped_swiglu_linear, grouped_uses_tc05, linear, swiglu_linear, xielu_linear
 
@@ -281,6 +282,143 @@ class MoeSwiGluShared(Part):
         return out
 
 
+def _relu2_mlp(rt, h, w_up, w_down, out, tag):
+    """out = down(relu(up h)^2)."""
+    z = rt.ws.get(tag + "_z", (h.shape[0], w_up.shape[0]), torch.float32)
+    linear(rt, h, w_up, z)
+    act = rt.ws.get(tag + "_act", (h.shape[0], w_up.shape[0]), rt.dtype)
+    ops.relu2(z, act)
+    linear(rt, act, w_down, out)
+    return out
+
+
+class ScaledInputMoe(Part):
+    """Router with sigmoid scores (32-bit), the top-k experts by score (ties to the lower id), weights = the chosen
+    scores as they are; a chosen expert works on weight * h: down_e(relu(up_e (w h))^2), which is computed as
+    relu(w (up_e h))^2 with the weight applied to the up-projection's 32-bit result; outputs are summed in ascending
+    expert id; a shared expert of the same form takes every token with weight one."""
+
+    graph_safe = True
+    wants_f32_input = True      # the router works from unrounded rows
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        if spec.activation != "relu2":
+            raise Unsupported("mlp.activation", f"{spec.activation!r}; experts of this kind square a relu")
+        self.w_router = self.w_up = self.w_down = self.w_shared_up = self.w_shared_down = None
+        self.expert_reads = rt.new_counter("expert_reads")
+
+    def _names(self):
+        s, p = self.spec, self.spec.prefix
+        experts = [(p + s.expert.format(e=e) + s.up, p + s.expert.format(e=e) + s.down) for e in range(s.num_experts)]
+        return p + s.router, (p + s.shared + s.up, p + s.shared + s.down), experts
+
+    def param_specs(self):
+        s = self.spec
+        router, shared, experts = self._names()
+        specs = [ParamSpec(router, (s.num_experts, s.hidden), "matrix")]
+        if s.shared_intermediate is not None:
+            specs += [ParamSpec(shared[0], (s.shared_intermediate, s.hidden), "matrix"),
+                      ParamSpec(shared[1], (s.hidden, s.shared_intermediate), "matrix")]
+        for up, down in experts:
+            specs += [ParamSpec(up, (s.expert_intermediate, s.hidden), "matrix"),
+                      ParamSpec(down, (s.hidden, s.expert_intermediate), "matrix")]
+        return specs
+
+    def allocate(self, stored, rt):
+        s, dev = self.spec, rt.device
+        E, Im, H = s.num_experts, s.expert_intermediate, s.hidden
+        router, shared, experts = self._names()
+        self.w_router = torch.empty((E, H), dtype=rt.matrix_dtype([stored[router]]), device=dev)
+        self.w_up = torch.empty((E, Im, H), dtype=rt.matrix_dtype([stored[u] for u, _d in experts]), device=dev)
+        self.w_down = torch.empty((E, H, Im), dtype=rt.matrix_dtype([stored[d] for _u, d in experts]), device=dev)
+        views = {router: self.w_router}
+        if s.shared_intermediate is not None:
+            self.w_shared_up = torch.empty((s.shared_intermediate, H), dtype=rt.matrix_dtype([stored[shared[0]]]), device=dev)
+            self.w_shared_down = torch.empty((H, s.shared_intermediate), dtype=rt.matrix_dtype([stored[shared[1]]]), device=dev)
+            views.update({shared[0]: self.w_shared_up, shared[1]: self.w_shared_down})
+        for e, (up, down) in enumerate(experts):
+            views[up] = self.w_up[e]
+            views[down] = self.w_down[e]
+        return views
+
+    def forward(self, h, ctx, h32=None):
+        rt = self.rt
+        n = h.shape[0]
+        y = rt.ws.get("ffn_out", (n, self.spec.hidden), torch.float32)
+        step = rt.ffn_chunk_tokens
+        for a in range(0, n, step):
+            b = min(n, a + step)
+            self._forward_rows(h[a:b], y[a:b], ctx, a, h32[a:b] if h32 is not None else h[a:b])
+        return y
+
+    def _forward_rows(self, h, y, ctx, row0, router_in):
+        s, rt = self.spec, self.rt
+        n, k, E, Im, H = h.shape[0], s.top_k, s.num_experts, s.expert_intermediate, s.hidden
+        ws = rt.ws
+        ids = ws.get("moe_ids", (n, k), torch.int32)
+        wts = ws.get("moe_w", (n, k), torch.float32)
+        probs = torch.empty((n, E), dtype=torch.float32, device=rt.device) if rt.record_routing else None
+        offsets = ws.get("moe_offsets", (E + 1,), torch.int32)
+        perm_token = ws.get("moe_perm_token", (n * k,), torch.int32)
+        perm_weight = ws.get("moe_perm_weight", (n * k,), torch.float32)
+        inverse = ws.get("moe_inverse", (n, k), torch.int32)
+        rows = n * k
+        tiles = None
+        if grouped_uses_tc05(h, self.w_up, rows, n) and Im % 16 == 0 and H % 16 == 0:
+            max_tiles = (rows + ops.TC05_TILE_ROWS - 1) // ops.TC05_TILE_ROWS + E
+            tiles = (ws.get("moe_tile_group", (max_tiles,), torch.int32), ws.get("moe_tile_row0", (max_tiles,), torch.int32),
+                     ws.get("moe_tile_count", (max_tiles,), torch.int32), ws.get("moe_n_tiles", (1,), torch.int32))
+        shared = None
+        beside = self.w_shared_up is not None and n <= SIDE_STREAM_ROWS and rt.side_stream is not None
+        if beside:
+            # few rows: the shared expert needs nothing of the routing and runs beside it on a second stream
+            shared = ws.get("moe_shared_out", (n, H), torch.float32)
+            main = torch.cuda.current_stream()
+            rt.side_stream.wait_stream(main)
+            with torch.cuda.stream(rt.side_stream):
+                _relu2_mlp(rt, h, self.w_shared_up, self.w_shared_down, shared, "moe_shared")
+        if n <= ops.ROUTE_SMALL_TOKENS and ops.route_small_fits(H, E):
+            logits = ws.get("moe_logits", (n, E + 1), torch.float32)
+            ops.route_small(router_in, self.w_router, None, logits, ids, wts, None, k, False, offsets, perm_token, perm_weight,
+                            inverse, rt.status, probs, distinct=self.expert_reads, tiles=tiles, sigmoid=True)
+        else:
+            ops.router_topk(router_in, self.w_router, None, ids, wts, None, k, False, rt.status, probs,
+                            logits=ws.get("moe_logits", (n, E + 1), torch.float32), sigmoid=True)
+            ops.moe_permute(ids, wts, E, offsets, perm_token, perm_weight, inverse, rt.status, tiles=tiles,
+                            distinct=self.expert_reads)
+        if rt.record_routing:
+            ctx.aux.setdefault("routing", []).append((s.prefix, row0, ids.clone(), wts.clone(), probs))
+        # routed experts: z = up_e h (32-bit result), act = relu(w z)^2, out = down_e act
+        z = ws.get("moe_z", (rows, Im), torch.float32)
+        act = ws.get("moe_act", (rows, Im), rt.dtype)
+        out = ws.get("moe_expert_out", (rows, H), torch.float32)
+        if tiles is not None:
+            gathered = ws.get("moe_gathered", (rows, H), torch.bfloat16)
+            ops.gather_rows(h, perm_token, gathered)
+            ops.gemm_tc05(gathered, self.w_up, z, rt.status, row_scale=perm_weight, tiles=tiles)
+            ops.relu2(z, act)
+            ops.gemm_tc05(act, self.w_down, out, rt.status, tiles=tiles)
+        elif h.dtype == torch.bfloat16 and self.w_up.dtype == torch.bfloat16 and self.w_down.dtype == torch.bfloat16 \
+                and ops.skinny_fits(H) and ops.skinny_fits(Im):
+            ops.gemm_skinny(h, self.w_up, z, a_rows=perm_token, row_scale=perm_weight, group_offsets=offsets, rows=rows, max_rows=n)
+            ops.relu2(z, act)
+            ops.gemm_skinny(act, self.w_down, out, group_offsets=offsets, rows=rows, max_rows=n)
+        else:
+            ops.gemm_simt(h, self.w_up, z, a_rows=perm_token, row_scale=perm_weight, group_offsets=offsets, rows=rows)
+            ops.relu2(z, act)
+            ops.gemm_simt(act, self.w_down, out, group_offsets=offsets, rows=rows)
+        if self.w_shared_up is not None:
+            if beside:
+                main.wait_stream(rt.side_stream)
+            else:
+                shared = ws.get("moe_shared_out", (n, H), torch.float32)
+                _relu2_mlp(rt, h, self.w_shared_up, self.w_shared_down, shared, "moe_shared")
+        ops.moe_combine(out, ids, inverse, None, shared, y)
+        return y
+
+
 register("ffn", "swiglu", DenseSwiGlu)
+register("ffn", "moe_sigmoid_scaled_input", ScaledInputMoe)
 register("ffn", "xielu", DenseXielu)
 register("ffn", "moe_swiglu_shared", MoeSwiGluShared)

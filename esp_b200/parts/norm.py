@@ -39,4 +39,43 @@ class RmsNorm(Part):
         return h
 
 
+class ScalarRmsNorm(RmsNorm):
+    """RMS norm whose weight is one number for all channels (a tensor without dimensions in the checkpoint).  The
+    number is spread over a vector once the weights are in, so the kernels of the vector form run it."""
+
+    def param_specs(self):
+        return [ParamSpec(self.spec.weight, (), "norm_scale")]
+
+    def allocate(self, stored, rt):
+        self.weight = torch.empty(self.spec.width, dtype=torch.float32, device=rt.device)
+        return {self.spec.weight: self.weight[0]}        # the loader fills the first entry; finalize copies it to all
+
+    def finalize(self):
+        if self.weight is not None:
+            self.weight.copy_(self.weight[0].clone().expand(self.spec.width))
+
+
+class DeferredPostNorm:
+    """A sublayer's result on its way into the residual stream through a norm of its own: x += norm(y).  The norm that
+    reads x next does that add and its own normalisation in one launch (``fused_add_rmsnorm``); anything else gets the
+    normed rows from ``materialize()``."""
+
+    def __init__(self, rt, y, norm):
+        self.rt, self.y, self.norm = rt, y, norm
+
+    def materialize(self):
+        out = self.rt.ws.get("post_normed", tuple(self.y.shape), torch.float32)
+        ops.norm_add_rmsnorm(None, self.y, self.norm.weight, self.norm.spec.eps, None, None, 0.0, h32=out)
+        return out
+
+    def fused_add_rmsnorm(self, x, gamma, h, eps, rows, write_x, h32):
+        ops.norm_add_rmsnorm(x, self.y, self.norm.weight, self.norm.spec.eps, gamma, h, eps, rows=rows, write_x=write_x,
+                             h32=h32)
+
+    def add_to(self, x):
+        """x += norm(y), nothing else."""
+        ops.norm_add_rmsnorm(x, self.y, self.norm.weight, self.norm.spec.eps, None, None, 0.0)
+
+
 register("norm", "rmsnorm", RmsNorm)
+register("norm", "rmsnorm_scalar", ScalarRmsNorm)

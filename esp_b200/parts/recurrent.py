@@ -191,5 +191,169 @@ class DecayBonusRecurrence(Part):
         return out
 
 
+class MatrixMemory(Part):
+    """Matrix memory with exponential gating (see ``MatrixMemorySpec``).  One packed product makes q, k, v, the output
+    gate and the two gate scalars per head; a short kernel turns the scalars into the running maximum m, the decay
+    exp(f + m' - m) and the input weight exp(i - m) (32-bit, a chain over the tokens) and lays out what the shared
+    recurrence kernel reads; the normaliser n rides along as one more value column whose value is always one.  Per
+    slot the state holds S and n as [heads, value columns, key channels] floats and then m per head."""
+
+    graph_safe = True
+    FLOOR = 1e-6                 # added to the denominator max(|n . q|, exp(-m))
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        _check_dims(spec.kind, spec.key_dim)
+        s = spec
+        self.kw, self.vw = s.num_heads * s.key_dim, s.num_heads * s.value_dim
+        self.cols = (s.value_dim + 1 + 3) // 4 * 4          # value columns of the recurrence: v, the one, zeros up to a multiple of 4
+        self.state_words = s.num_heads * self.cols * s.key_dim
+        self.proj_width = 2 * self.kw + 2 * self.vw + 2 * s.num_heads
+        self.w_in = self.w_o = self.gate_bias = self.norm_w = None
+
+    def _n(self, which):
+        return self.spec.prefix + getattr(self.spec.names, which)
+
+    def param_specs(self):
+        s = self.spec
+        return [ParamSpec(self._n("q"), (self.kw, s.hidden), "matrix"), ParamSpec(self._n("k"), (self.kw, s.hidden), "matrix"),
+                ParamSpec(self._n("v"), (self.vw, s.hidden), "matrix"), ParamSpec(self._n("gate"), (self.vw, s.hidden), "matrix"),
+                ParamSpec(self._n("input_gate"), (s.num_heads, s.hidden), "matrix"),
+                ParamSpec(self._n("input_gate") + ".b", (s.num_heads,), "bias"),
+                ParamSpec(self._n("forget_gate"), (s.num_heads, s.hidden), "matrix"),
+                ParamSpec(self._n("forget_gate") + ".b", (s.num_heads,), "forget_bias", init=(2.0, 1.0)),
+                ParamSpec(self._n("norm"), (self.vw,), "norm_scale"),
+                ParamSpec(self._n("o"), (s.hidden, self.vw), "matrix")]
+
+    def allocate(self, stored, rt):
+        s, dev = self.spec, rt.device
+        order = ["q", "k", "v", "gate", "input_gate", "forget_gate"]
+        names = [self._n(t) for t in order]
+        sizes = [self.kw, self.kw, self.vw, self.vw, s.num_heads, s.num_heads]
+        self.w_in = torch.empty((self.proj_width, s.hidden), dtype=rt.matrix_dtype([stored[n] for n in names]), device=dev)
+        self.w_o = torch.empty((s.hidden, self.vw), dtype=rt.matrix_dtype([stored[self._n("o")]]), device=dev)
+        self.gate_bias = torch.empty((2, s.num_heads), dtype=torch.float32, device=dev)
+        self.norm_w = torch.empty(self.vw, dtype=torch.float32, device=dev)
+        views, at = {}, 0
+        self.cols_at = {}
+        for t, n, size in zip(order, names, sizes):
+            views[n] = self.w_in[at:at + size]
+            self.cols_at[t] = (at, at + size)
+            at += size
+        views.update({self._n("input_gate") + ".b": self.gate_bias[0], self._n("forget_gate") + ".b": self.gate_bias[1],
+                      self._n("norm"): self.norm_w, self._n("o"): self.w_o})
+        return views
+
+    def kv_layout(self):
+        return None
+
+    def state_spec(self):
+        return StateSpec((self.state_words + self.spec.num_heads,), torch.float32)
+
+    def forward(self, h, ctx, layer):
+        s, rt = self.spec, self.rt
+        n, H = h.shape[0], s.num_heads
+        proj = rt.ws.get("mm_proj", (n, self.proj_width), torch.float32)
+        linear(rt, h, self.w_in, proj)
+        part = lambda t: proj[:, self.cols_at[t][0]:self.cols_at[t][1]]
+        qkd = rt.ws.get("rec_gates", (3, n, self.kw), torch.float32)
+        v1 = rt.ws.get("mm_values", (n, H * self.cols), torch.float32)
+        m = rt.ws.get("mm_max", (n, H), torch.float32)
+        ops.matrix_memory_prepare(part("q"), part("k"), part("v"), part("input_gate"), part("forget_gate"), self.proj_width,
+                                  self.gate_bias[0], self.gate_bias[1], s.gate_cap, s.key_dim ** -0.5,
+                                  layer.state[:, self.state_words:], ctx.seq_start, ctx.seq_slot, qkd[0], qkd[1], qkd[2], v1, m,
+                                  ctx.n_seqs, H, s.key_dim, s.value_dim, self.cols)
+        o = rt.ws.get("rec_out", (n, H * self.cols), torch.float32)
+        ops.gated_scan(ops.SCAN_LOWER_SIGMOID, qkd[0], qkd[1], qkd[2], v1, None, None, None, layer.state, ctx.seq_start,
+                       ctx.seq_slot, o, ctx.n_seqs, H, s.key_dim, self.cols, ready=True)
+        y = rt.ws.get("rec_normed", (n, self.vw), rt.dtype)
+        ops.matrix_memory_finish(o, m, self.norm_w, part("gate"), y, H, s.value_dim, self.cols, s.eps, self.FLOOR)
+        out = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
+        linear(rt, y, self.w_o, out)
+        return out
+
+
+class GatedDiagonalRecurrence(Part):
+    """Recurrent block with a real-gated diagonal recurrence (see ``GatedDiagonalSpec``).  One packed product makes
+    both branches; a kernel applies GELU to the gate branch and the causal convolution to the other (the last taps - 1
+    inputs of a sequence are state); the recurrence and input gates are block-diagonal projections of the
+    convolution's output (one per-block product for both); a scan kernel makes the decay and walks the tokens.  Per
+    slot the state holds S [channels] and then the convolution's inputs [taps - 1, channels], all floats."""
+
+    graph_safe = True
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        s = spec
+        if s.channels % s.blocks:
+            raise Unsupported(s.kind + ".blocks", f"{s.blocks} does not divide {s.channels} channels")
+        if s.taps > ops.CONV_MAX_TAPS:
+            raise Unsupported(s.kind + ".conv", f"{s.taps} taps; the convolution kernel takes up to {ops.CONV_MAX_TAPS}")
+        self.cb = s.channels // s.blocks
+        if self.cb * 8 * 4 > 48 * 1024:
+            raise Unsupported(s.kind + ".blocks", f"blocks of {self.cb} channels are beyond what the per-block product takes")
+        self.w_in = self.b_in = self.conv_w = self.conv_b = self.w_gates = self.b_gates = self.lam = self.w_o = None
+
+    def _n(self, which):
+        return self.spec.prefix + getattr(self.spec.names, which)
+
+    def param_specs(self):
+        s, C, B, cb = self.spec, self.spec.channels, self.spec.blocks, self.cb
+        return [ParamSpec(self._n("gate_branch"), (C, s.hidden), "matrix"), ParamSpec(self._n("gate_branch") + ".b", (C,), "bias"),
+                ParamSpec(self._n("in_branch"), (C, s.hidden), "matrix"), ParamSpec(self._n("in_branch") + ".b", (C,), "bias"),
+                ParamSpec(self._n("conv"), (C, s.taps), "conv_taps", init=(0.0, 0.5)),
+                ParamSpec(self._n("conv") + ".b", (C,), "bias"),
+                ParamSpec(self._n("recurrence_gate"), (B, cb, cb), "gate_matrix", init=(0.0, 0.2)),
+                ParamSpec(self._n("recurrence_gate") + ".b", (B, cb), "bias"),
+                ParamSpec(self._n("input_gate"), (B, cb, cb), "gate_matrix", init=(0.0, 0.2)),
+                ParamSpec(self._n("input_gate") + ".b", (B, cb), "bias"),
+                ParamSpec(self._n("decay"), (C,), "decay_rate", init=(-1.0, 1.0)),
+                ParamSpec(self._n("o"), (s.hidden, C), "matrix")]
+
+    def allocate(self, stored, rt):
+        s, dev, C, B, cb = self.spec, rt.device, self.spec.channels, self.spec.blocks, self.cb
+        f32 = lambda *shape: torch.empty(shape, dtype=torch.float32, device=dev)
+        ny, nx = self._n("gate_branch"), self._n("in_branch")
+        self.w_in = torch.empty((2 * C, s.hidden), dtype=rt.matrix_dtype([stored[ny], stored[nx]]), device=dev)
+        self.b_in = f32(2, C)
+        self.conv_w, self.conv_b = f32(C, s.taps), f32(C)
+        nr, ni = self._n("recurrence_gate"), self._n("input_gate")
+        # a block's two gate matrices stacked: one per-block product makes [r | i] of the block
+        self.w_gates = torch.empty((B, 2 * cb, cb), dtype=rt.matrix_dtype([stored[nr], stored[ni]]), device=dev)
+        self.b_gates = f32(2, C)
+        self.lam = f32(C)
+        self.w_o = torch.empty((s.hidden, C), dtype=rt.matrix_dtype([stored[self._n("o")]]), device=dev)
+        return {ny: self.w_in[:C], nx: self.w_in[C:], ny + ".b": self.b_in[0], nx + ".b": self.b_in[1],
+                self._n("conv"): self.conv_w, self._n("conv") + ".b": self.conv_b, nr: self.w_gates[:, :cb], ni: self.w_gates[:, cb:],
+                nr + ".b": self.b_gates[0].view(B, cb), ni + ".b": self.b_gates[1].view(B, cb), self._n("decay"): self.lam,
+                self._n("o"): self.w_o}
+
+    def kv_layout(self):
+        return None
+
+    def state_spec(self):
+        return StateSpec((self.spec.taps * self.spec.channels,), torch.float32)
+
+    def forward(self, h, ctx, layer):
+        s, rt, C = self.spec, self.rt, self.spec.channels
+        n = h.shape[0]
+        proj = rt.ws.get("diag_proj", (n, 2 * C), torch.float32)
+        linear(rt, h, self.w_in, proj)
+        branch = rt.ws.get("diag_branch", (2, n, C), torch.float32)        # the gate branch, the convolution's output
+        u_act = rt.ws.get("diag_u", (n, C), rt.dtype)
+        ops.conv_branches(proj, self.b_in[0], self.b_in[1], self.conv_w, self.conv_b, layer.state[:, C:], ctx.tok_seq,
+                          ctx.seq_start, ctx.seq_slot, branch[0], branch[1], u_act, ctx.n_seqs, C, s.taps)
+        gates = rt.ws.get("diag_gates", (n, 2 * C), torch.float32)
+        ops.per_head_linear(u_act, C, self.cb, self.w_gates, gates, 2 * C, 2 * self.cb, n, s.blocks, self.cb, 2 * self.cb)
+        y = rt.ws.get("rec_normed", (n, C), rt.dtype)
+        ops.diag_scan(gates, self.b_gates[0], self.b_gates[1], self.lam, s.decay_scale, branch[1], branch[0], layer.state,
+                      ctx.seq_start, ctx.seq_slot, y, ctx.n_seqs, C, s.blocks)
+        out = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
+        linear(rt, y, self.w_o, out)
+        return out
+
+
 register("mixer", "hgrn2", LowerBoundRecurrence)
+register("mixer", "mlstm", MatrixMemory)
+register("mixer", "rglru", GatedDiagonalRecurrence)
 register("mixer", "wkv", DecayBonusRecurrence)
