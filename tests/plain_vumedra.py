@@ -60,6 +60,24 @@ def embedding(tokens, w, cfg, dtype, first_position=0, before=None):
 
 
 # ---------------------------------------------------------------------------------------------------------
+def attend_with_sink(q, k, v, scale, q_pos, k_pos, sink=True):
+    """q [Tq, H, K], k [Tk, G, K], v [Tk, G, V]: causal by the positions given; with ``sink`` the denominator is
+    1 + sum exp(s).  Returns [Tq, H, V]."""
+    H, G = q.shape[1], k.shape[1]
+    out = torch.zeros(q.shape[0], H, v.shape[2], dtype=q.dtype)
+    for head in range(H):
+        g = head // (H // G)
+        s = (q[:, head] @ k[:, g].T) * scale
+        s = s.masked_fill(k_pos[None, :] > q_pos[:, None], float("-inf"))
+        if sink:
+            e = torch.exp(s)
+            p = e / (1 + e.sum(-1, keepdim=True))
+        else:
+            p = torch.softmax(s, -1)
+        out[:, head] = p @ v[:, g]
+    return out
+
+
 def sink_attention(h, w, pre, mix, eps, positions):
     """Causal softmax attention whose denominator holds one more term, exp(0): a key that every query sees,
     with score zero and no value.  Queries and keys are RMS-normed per head; the query grows with the
@@ -76,13 +94,7 @@ def sink_attention(h, w, pre, mix, eps, positions):
     if temp:
         steps = torch.floor((positions.to(torch.float64) + 1) / temp["every"])
         q = q * (1 + temp["coef"] * torch.log(steps + 1)).to(h.dtype)[:, None, None]
-    out = torch.zeros(T, H, V, dtype=h.dtype)
-    for head in range(H):
-        g = head // (H // G)
-        s = (q[:, head] @ k[:, g].T) * mix["scale"]
-        s = s.masked_fill(positions[None, :] > positions[:, None], float("-inf"))
-        e = torch.exp(s)
-        out[:, head] = (e / (1 + e.sum(-1, keepdim=True))) @ v[:, g]
+    out = attend_with_sink(q, k, v, mix["scale"], positions, positions)
     return out.reshape(T, H * V) @ w[pre + "o"].T
 
 
@@ -232,3 +244,13 @@ def tensor_shapes(cfg):
             if mlp.get("shared") is not None:
                 out.update({p + "shared.up": (mlp["shared"]["ff"], D), p + "shared.down": (D, mlp["shared"]["ff"])})
     return out
+
+
+def greedy(cfg, weights, prompt, count):
+    """``count`` greedy tokens after ``prompt`` and, for each, the margin between the best and the second logit."""
+    seq, margins = list(prompt), []
+    for _ in range(count):
+        top = torch.topk(forward(cfg, weights, seq)[-1], 2)
+        margins.append(float(top.values[0] - top.values[1]))
+        seq.append(int(top.indices[0]))
+    return seq[len(prompt):], margins
