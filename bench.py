@@ -468,6 +468,36 @@ def dense_qwen2_config(width, ff, layers, vocab):
                 mlp_only_layers=list(range(layers)), max_position_embeddings=8192)
 
 
+# --design vumedra: the decoder with a matrix memory, a gated diagonal recurrence, attention with a sink and routed
+# experts that scale their input, beside the Qwen2 MoE decoder of the same width, depth, heads, dense and expert sizes
+# (dense feed-forwards in the even layers, routed experts with a shared expert in the odd ones, as the design has them).
+VUMEDRA_EXPERTS, VUMEDRA_TOP = 16, 2
+
+
+def vumedra_config(width, ff, layers, vocab):
+    heads = width // 128
+    pattern = [{"type": "mlstm", "mixer": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "gate_cap": 15.0}},
+               {"type": "rglru", "mixer": {"width": width, "blocks": heads, "conv": 4}},
+               {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128,
+                                               "scale": 128 ** -0.5, "q_temp": {"coef": 0.1, "every": 1024}}},
+               {"type": "mlstm", "mixer": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "gate_cap": 15.0}}]
+    moe = {"kind": "moe", "router": {"experts": VUMEDRA_EXPERTS, "top": VUMEDRA_TOP}, "expert": {"ff": ff // 4},
+           "shared": {"ff": ff // 2}}
+    out = [{"type": pattern[i % 4]["type"], "mixer": dict(pattern[i % 4]["mixer"]),
+            "mlp": dict(moe) if i % 2 else {"kind": "dense", "ff": ff}} for i in range(layers)]
+    return {"architecture": "Vumedra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": out}
+
+
+def sparse_qwen2_config(width, ff, layers, vocab):
+    heads = width // 128
+    return dict(A27B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=max(1, heads // 4), head_dim=128, vocab_size=vocab, intermediate_size=ff,
+                num_experts=VUMEDRA_EXPERTS, num_experts_per_tok=VUMEDRA_TOP, moe_intermediate_size=ff // 4,
+                shared_expert_intermediate_size=ff // 2, decoder_sparse_step=1,
+                mlp_only_layers=list(range(0, layers, 2)), max_position_embeddings=8192)
+
+
 def measure_design(torch, raw, prefill_tokens, batches, context, steps, warmup, clocks):
     """Prefill of one prompt and decode steps of a model with random weights: tokens per second, and device time
     by kind of kernel for one eager prefill and one eager decode step (library products count with the kernel
@@ -524,17 +554,21 @@ def bench_design(torch, a, pk):
     sizes = {"w1024": (1024, 2816, 8), "w2048": (2048, 5632, 8), "w4096": (4096, 11008, 8)}
     picked = [s for s in a.design_sizes.split(",") if s]
     vocab, window = 32768, 4096
-    result = {"design": "zusepel", "beside": "dense Qwen2 decoder of equal width, depth and feed-forward width", "dtype": "bf16",
+    vumedra = a.design == "vumedra"
+    beside = ("Qwen2 MoE decoder of equal width, depth, heads, dense and expert sizes" if vumedra else
+              "dense Qwen2 decoder of equal width, depth and feed-forward width")
+    result = {"design": a.design, "beside": beside, "dtype": "bf16",
               "data": "synthetic token ids, random weights N(0,0.02)", "prefill_tokens": a.prefill_tokens,
               "context": a.context, "steps": a.steps, "warmup": max(3, a.warmup), "peaks": pk, "sizes": {}}
     clocks = ClockSampler()
     for name in picked:
         width, ff, layers = sizes[name]
         entry = {"width": width, "ff": ff, "layers": layers, "vocab": vocab}
-        entry["zusepel"] = measure_design(torch, zusepel_config(width, ff, layers, vocab, window), a.prefill_tokens, (1, 8),
-                                          a.context, a.steps, a.warmup, clocks)
-        entry["qwen2_dense"] = measure_design(torch, dense_qwen2_config(width, ff, layers, vocab), a.prefill_tokens,
-                                              (1, 8), a.context, a.steps, a.warmup, clocks)
+        mine = vumedra_config(width, ff, layers, vocab) if vumedra else zusepel_config(width, ff, layers, vocab, window)
+        other = sparse_qwen2_config(width, ff, layers, vocab) if vumedra else dense_qwen2_config(width, ff, layers, vocab)
+        entry[a.design] = measure_design(torch, mine, a.prefill_tokens, (1, 8), a.context, a.steps, a.warmup, clocks)
+        entry["qwen2_moe" if vumedra else "qwen2_dense"] = measure_design(torch, other, a.prefill_tokens, (1, 8), a.context,
+                                                                          a.steps, a.warmup, clocks)
         result["sizes"][name] = entry
     result["clocks"] = clocks.summary()
     print(json.dumps(result))
@@ -543,9 +577,9 @@ def bench_design(torch, a, pk):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["zusepel"],
+    ap.add_argument("--design", default=None, choices=["zusepel", "vumedra"],
                     help="instead of the default workload: prefill and decode of this design at a few layer sizes, beside "
-                         "the dense Qwen2 decoder of equal size")
+                         "the closest Qwen2 decoder of equal size (dense for zusepel, with routed experts for vumedra)")
     ap.add_argument("--design-sizes", default="w1024,w2048", help="with --design: which of w1024, w2048, w4096")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)

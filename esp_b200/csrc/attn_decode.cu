@@ -90,7 +90,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
                       const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
                       int* __restrict__ counters, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                       const int* __restrict__ seq_past, const int* __restrict__ block_table, int table_stride, int n_pages,
-                      int page, int nh, int nkv, int window, int split_keys, int n_splits, int* __restrict__ status) {
+                      int page, int nh, int nkv, int window, int split_keys, int n_splits, float score_scale, int sink,
+                      int* __restrict__ status) {
     pdl_trigger();
     constexpr int ITEM = PAGE_KEYS * HD;
     constexpr int NBW = HD / 32;                   // 8-column blocks of the head that one warp accumulates
@@ -201,7 +202,7 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
             for (int j = 0; j < 4; j++) {
                 const int t = warp * 16 + nb * 8 + tg * 2 + (j & 1), key = key0 + t;
                 const bool live = page_ok && key >= j0 && key <= j1;
-                if (g8 + (j >> 1) * 8 < heads) s_s[g8 + (j >> 1) * 8][t] = live ? sc[nb][j] / root : -INFINITY;
+                if (g8 + (j >> 1) * 8 < heads) s_s[g8 + (j >> 1) * 8][t] = live ? (score_scale > 0.f ? sc[nb][j] * score_scale : sc[nb][j] / root) : -INFINITY;
             }
         __syncthreads();                           // scores are written; the key buffer is free
         if (tid == 0 && issued < n_items) issue(issued++);
@@ -317,7 +318,8 @@ attn_split_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         for (int sp = s0 + lane; sp <= s1; sp += 32) mx = fmaxf(mx, __ldcg(ml + 2 * sp));
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-        float denom = 0.f, num[NV][2];
+        if (sink) mx = fmaxf(mx, 0.f);                     // one more key of score zero, without a value
+        float denom = sink ? expf(-mx) : 0.f, num[NV][2];
 #pragma unroll
         for (int j = 0; j < NV; j++) num[j][0] = num[j][1] = 0.f;
         for (int c0 = s0; c0 <= s1; c0 += WCH) {
@@ -379,7 +381,8 @@ int make_cache_map(CUtensorMap* map, const void* base, unsigned long long rows, 
 template <int HD>
 int launch_split_mma(int split, const bf16* q, const bf16* k, const bf16* v, bf16* out, float* po, float* pml, int* counters,
                      const int* tok_seq, const int* tok_pos, const int* seq_past, const int* table, int stride, int n_pages, int page,
-                     int n_tokens, int nh, int nkv, int window, int n_splits, int* status, cudaStream_t stream) {
+                     int n_tokens, int nh, int nkv, int window, int n_splits, float score_scale, int sink, int* status,
+                     cudaStream_t stream) {
     CUtensorMap map_k, map_v;
     const unsigned long long rows = (unsigned long long)n_pages * nkv * PAGE_KEYS;
     int rc = make_cache_map(&map_k, k, rows, HD);
@@ -398,7 +401,8 @@ int launch_split_mma(int split, const bf16* q, const bf16* k, const bf16* v, bf1
     const int group = nh / nkv;
     dim3 grid(n_tokens, nkv * ((group + MMA_HEADS - 1) / MMA_HEADS), n_splits);
     esp_launch_pdl(ESP_PDL_ATTENTION, attn_split_mma_kernel<HD>, dim3(grid), dim3(THREADS), dyn, stream, map_k, map_v, q, out, po, pml,
-                   counters, tok_seq, tok_pos, seq_past, table, stride, n_pages, page, nh, nkv, window, split, n_splits, status);
+                   counters, tok_seq, tok_pos, seq_past, table, stride, n_pages, page, nh, nkv, window, split, n_splits, score_scale,
+                   sink, status);
     return esp_launch_status();
 }
 }  // namespace
@@ -409,18 +413,20 @@ int launch_split_mma(int split, const bf16* q, const bf16* k, const bf16* v, bf1
 // that every SM still gets blocks); n_splits >= ceil(longest sequence / split).  Head sizes 64, 128, 192, 256; pages of 64 positions or any
 // size; any head counts with nh % nkv == 0.  ``seq_past`` (may be null): per sequence of the step, the positions
 // that were cached before it; with it, blocks whose keys are all older start their loads without waiting for the
-// kernel before this one.
+// kernel before this one.  score_scale > 0 multiplies the scores (else they are divided by sqrt(hd)); ``sink``: the
+// softmax's denominator holds one more term exp(0).
 ESP_API int esp_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o,
                             float* part_ml, int* counters, const int* tok_seq, const int* tok_pos, const int* seq_past,
                             const int* block_table, int table_stride, int n_pages, int page, int n_tokens, int nh, int nkv,
-                            int hd, int window, int split, int n_splits, int* status, cudaStream_t stream) {
+                            int hd, int window, int split, int n_splits, float score_scale, int sink, int* status,
+                            cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (nkv <= 0 || nh % nkv != 0 || n_splits <= 0 || n_splits > 65535 || nh > 65535 || split < PAGE_KEYS || split % PAGE_KEYS != 0 ||
         page != PAGE_KEYS)
         return (int)cudaErrorInvalidValue;
 #define ESP_HD(HD) return launch_split_mma<HD>(split, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, part_o, \
                                                part_ml, counters, tok_seq, tok_pos, seq_past, block_table, table_stride, n_pages, \
-                                               page, n_tokens, nh, nkv, window, n_splits, status, stream)
+                                               page, n_tokens, nh, nkv, window, n_splits, score_scale, sink, status, stream)
     switch (hd) {
         case 64: ESP_HD(64);
         case 128: ESP_HD(128);
@@ -477,5 +483,5 @@ extern "C" int esp_attn_decode_noalloc(const void* q, const void* k_cache, const
     float* part_ml = part_o + (size_t)n_tokens * nh * n_splits * hd;
     int* counters = reinterpret_cast<int*>(noalloc_scratch_of_device[device] + esp_attn_decode_noalloc_capacity());
     return esp_attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, nullptr, block_table, table_stride,
-                           n_pages, page, n_tokens, nh, nkv, hd, window, split, n_splits, status, stream);
+                           n_pages, page, n_tokens, nh, nkv, hd, window, split, n_splits, 0.f, 0, status, stream);
 }

@@ -50,6 +50,8 @@ struct AttnParams {
     const int* block_table;
     int table_stride, n_pages, nh, nkv, window, kv_rows, n_tiles, smem_bytes;
     int* status;
+    float scale;      // > 0: multiplies the scores; else they are divided by sqrt(head size)
+    int sink;         // the softmax's denominator holds one more term, a key of score zero without a value
 };
 
 // instruction descriptor: bfloat16 x bfloat16 -> float, M = 128, N = n, A K-major, B K-major or MN-major
@@ -301,7 +303,7 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         // meet at a named barrier of their own (once when all have written, once when all have read).
         const int quad = warp & 3, r = quad * 32 + lane, grp = (warp - 2) / (4 * ROWT), side = ((warp - 2) >> 2) % ROWT;
         const unsigned lane_sel = (unsigned)(quad * 32) << 16;
-        const float sc = 1.4426950408889634f / sqrtf((float)HD);
+        const float sc = 1.4426950408889634f * (p.scale > 0.f ? p.scale : 1.0f / sqrtf((float)HD));
         constexpr int CW = BN / ROWT;                                    // keys of a block that this thread takes
         constexpr int OW = HD / ROWT;                                    // columns of the group's O that this thread rescales
         constexpr int FW = HD / (GROUPS * ROWT);                         // columns of the result that this thread writes
@@ -418,12 +420,14 @@ attn_prefill_tc05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             float m_all = -INFINITY, f[GROUPS], l_all = 0.f;
 #pragma unroll
             for (int b = 0; b < GROUPS; b++) m_all = fmaxf(m_all, xchg[b * (ROWT * 128) + 128 + r]);
+            if (p.sink) m_all = fmaxf(m_all, 0.f);                        // the sink's score is zero
 #pragma unroll
             for (int b = 0; b < GROUPS; b++) {                            // a group without a key for this row counts 0
                 const float m_b = xchg[b * (ROWT * 128) + 128 + r];
                 f[b] = m_b == -INFINITY ? 0.f : fast_exp2(m_b - m_all);
                 l_all += f[b] * xchg[b * (ROWT * 128) + r];
             }
+            if (p.sink) l_all += fast_exp2(-m_all);
             const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
             const int col0 = (grp * ROWT + side) * FW;
             float o[FW];
@@ -530,7 +534,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, 
 ESP_API int esp_attn_prefill_tc05(const void* q, long long n_tokens, const void* k_cache, const void* v_cache, void* out,
                                   const int* tile_seq, const int* tile_first, const int* seq_start, const int* seq_past,
                                   const int* block_table, int table_stride, int n_pages, int page, int n_tiles, int nh,
-                                  int nkv, int hd, int window, int* status, cudaStream_t stream) {
+                                  int nkv, int hd, float scale, int sink, int window, int* status, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (page != PAGE || (hd != 64 && hd != 128) || nkv <= 0 || nh % nkv != 0 || nh > 65535 || n_tokens <= 0)
         return (int)cudaErrorInvalidValue;
@@ -544,7 +548,7 @@ ESP_API int esp_attn_prefill_tc05(const void* q, long long n_tokens, const void*
     rc = make_map2d(&mv, v_cache, (unsigned long long)hd, kv_rows, PAGE);
     if (rc) return rc;
     AttnParams p{(bf16*)out, tile_seq, tile_first, seq_start, seq_past, block_table, table_stride, n_pages, nh, nkv,
-                 window, (int)kv_rows, n_tiles, 0, status};
+                 window, (int)kv_rows, n_tiles, 0, status, scale, sink};
     if (hd == 64) return launch<64>(mq, mk, mv, p, n_tiles, stream);
     return launch<128>(mq, mk, mv, p, n_tiles, stream);
 }

@@ -513,11 +513,85 @@ __global__ void norm_add_rmsnorm_kernel(float* __restrict__ x, const float* __re
     }
 }
 
+// Same operation for rows whose width is a multiple of 4 and at most 4 * 4 * 1024: each thread keeps up to four
+// float4 pieces of y and of x in registers, so both are read once.  Sums of squares per thread in piece order,
+// combined by the same fixed tree.  (x given; h may be null.)
+template <typename TH>
+__global__ void __launch_bounds__(1024)
+norm_add_rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ gamma_y,
+                             float eps_y, const float* __restrict__ gamma, const int* __restrict__ rows,
+                             TH* __restrict__ h, float* __restrict__ h32, int width, float eps, int write_x) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    const int pieces = width / 4;
+    float4* xr = reinterpret_cast<float4*>(x + s * width);
+    const float4* yr = reinterpret_cast<const float4*>(y + s * width);
+    float4 v[4], a[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < pieces) {
+            a[i] = yr[q];
+            v[i] = xr[q];
+            ss = fmaf(a[i].x, a[i].x, ss);
+            ss = fmaf(a[i].y, a[i].y, ss);
+            ss = fmaf(a[i].z, a[i].z, ss);
+            ss = fmaf(a[i].w, a[i].w, ss);
+        }
+    }
+    const float inv_y = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps_y);
+    ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < pieces) {
+            const float4 gy = reinterpret_cast<const float4*>(gamma_y)[q];
+            v[i].x += a[i].x * inv_y * gy.x; v[i].y += a[i].y * inv_y * gy.y;
+            v[i].z += a[i].z * inv_y * gy.z; v[i].w += a[i].w * inv_y * gy.w;
+            if (write_x) xr[q] = v[i];
+            ss = fmaf(v[i].x, v[i].x, ss);
+            ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss);
+            ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    if (!h) return;
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < pieces) {
+            const float4 gm = reinterpret_cast<const float4*>(gamma)[q];
+            const float o0 = v[i].x * inv * gm.x, o1 = v[i].y * inv * gm.y, o2 = v[i].z * inv * gm.z, o3 = v[i].w * inv * gm.w;
+            Vec4<TH>::store(h + (size_t)r * width + 4 * q, o0, o1, o2, o3);
+            if (h32) reinterpret_cast<float4*>(h32 + (size_t)r * width)[q] = make_float4(o0, o1, o2, o3);
+        }
+    }
+}
+
 ESP_API int esp_norm_add_rmsnorm(float* x, const float* y, const float* gamma_y, float eps_y, const float* gamma,
                                  const int* rows, void* h, int h_is_bf16, float* h32, int n_rows, int width, float eps,
                                  int write_x, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (!y || !gamma_y || (!x && !h32) || (h && !gamma)) return (int)cudaErrorInvalidValue;
+    if (x && width % 4 == 0 && width <= 16384) {
+        // one piece per thread while a block can hold them (the thread count depends on the width alone in the 32-bit
+        // path, so a row's sums have one order whatever else is in the step); many rows rounded to bfloat16: four
+        // pieces per thread, smaller blocks, more rows in flight per SM
+        int threads = ((width / 4 + 3) / 4 + 31) / 32 * 32;
+        if (width / 4 <= 1024 && !(h_is_bf16 && n_rows >= 256)) threads = (width / 4 + 31) / 32 * 32;
+        if (h_is_bf16)
+            esp_launch_pdl(ESP_PDL_SMALL, norm_add_rmsnorm_rows_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, y,
+                           gamma_y, eps_y, gamma, rows, (bf16*)h, h32, width, eps, write_x);
+        else
+            esp_launch_pdl(ESP_PDL_SMALL, norm_add_rmsnorm_rows_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, y,
+                           gamma_y, eps_y, gamma, rows, (float*)h, h32, width, eps, write_x);
+        return esp_launch_status();
+    }
     const int threads = width >= 2048 ? 512 : width >= 512 ? 256 : 128;
     if (h_is_bf16)
         esp_launch_pdl(ESP_PDL_SMALL, norm_add_rmsnorm_kernel<bf16>, dim3(n_rows), dim3(threads), 0, stream, x, y, gamma_y,

@@ -37,6 +37,7 @@ struct SkinnyParams {
     const int* group_offsets;
     const float* row_scale;
     const float* act_pq;            // plain form only: null, or the two raw numbers of an xIELU applied to every output
+    int act_relu2;                  // plain form only: every output (after its row's scale) becomes max(v, 0)^2
     void* C;
     long long ldc;
     int M, N, K;
@@ -283,6 +284,10 @@ gemm_skinny_kernel(SkinnyParams p) {
                             v_lo = skinny_xielu(v_lo, ap, an);
                             v_hi = skinny_xielu(v_hi, ap, an);
                         }
+                        if (p.act_relu2) {
+                            v_lo = fmaxf(v_lo, 0.f); v_lo *= v_lo;
+                            v_hi = fmaxf(v_hi, 0.f); v_hi *= v_hi;
+                        }
                         if (n_lo < p.N) reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n_lo] = from_f32<TC>(v_lo);
                         if (n_hi < p.N) reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n_hi] = from_f32<TC>(v_hi);
                     }
@@ -327,6 +332,7 @@ gemm_skinny_kernel(SkinnyParams p) {
                 if (tok < cnt && n < p.N) {
                     if (p.row_scale) v *= p.row_scale[m0 + tok];
                     if (p.act_pq) v = skinny_xielu(v, skinny_softplus(p.act_pq[0]), 0.5f + skinny_softplus(p.act_pq[1]));
+                    if (p.act_relu2) { v = fmaxf(v, 0.f); v *= v; }
                     reinterpret_cast<TC*>(p.C)[(size_t)(m0 + tok) * p.ldc + n] = from_f32<TC>(v);
                 }
             }
@@ -390,15 +396,19 @@ int launch(const SkinnyParams& p, int groups, cudaStream_t stream) {
 // ``max_rows``: an upper bound of the rows of any one group (of M when dense); it
 // selects how many rows are staged at a time.  swiglu: N is the intermediate
 // size and W holds 2N rows per group.  c_dtype: 0 float, 1 bfloat16.  act_pq (plain form): null, or two floats on the
-// device: every output passes through the xIELU they parameterise.
+// device: every output passes through the xIELU they parameterise.  swiglu = 2: the plain form whose outputs, after
+// the row's scale, become max(v, 0)^2.
 ESP_API int esp_gemm_skinny(const void* A, long long lda, const int* a_rows, const void* W, long long w_group_stride,
                             const float* row_scale, void* C, int c_dtype, long long ldc, const int* group_offsets,
                             int groups, int M, int N, int K, int max_rows, int swiglu, int offsets_ready, const float* act_pq,
                             cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K % 8 != 0 || lda % 8 != 0 || groups > 65535 || (swiglu && act_pq)) return (int)cudaErrorInvalidValue;
+    const int relu2 = swiglu == 2 ? 1 : 0;
+    if (relu2) swiglu = 0;
+    if (K % 8 != 0 || lda % 8 != 0 || groups > 65535 || ((swiglu || relu2) && act_pq)) return (int)cudaErrorInvalidValue;
     SkinnyParams p{};
     p.act_pq = act_pq;
+    p.act_relu2 = relu2;
     p.offsets_ready = group_offsets && offsets_ready ? 1 : 0;
     p.W = (const bf16*)W; p.w_group_stride = w_group_stride; p.A = (const bf16*)A; p.lda = lda; p.a_rows = a_rows;
     p.group_offsets = group_offsets; p.row_scale = row_scale; p.C = C; p.ldc = ldc; p.M = M; p.N = N; p.K = K;

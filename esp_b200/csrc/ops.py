@@ -53,11 +53,11 @@ _SIGNATURES = {
     "esp_relu2": [P, P, P, c_int, c_longlong, c_int, P],
     "esp_qknorm_kvwrite": [P, P, P, P, c_float, c_float, c_int, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, P, P],
-    "esp_matrix_memory_prepare": [P, P, P, P, P, c_longlong, P, P, c_float, c_float, P, c_longlong, P, P, P, P, P, P, P, c_int,
-                                  c_int, c_int, c_int, c_int, P],
-    "esp_matrix_memory_finish": [P, P, P, P, c_longlong, P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, P],
+    "esp_matrix_memory_prepare": [P, P, P, c_longlong, P, P, c_float, P, c_longlong, P, P, P, P, c_int, c_int, c_int, c_int,
+                                  c_int, P],
+    "esp_matrix_memory_finish": [P, P, P, P, c_longlong, P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, P],
     "esp_conv_branches": [P, P, P, P, P, P, c_longlong, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
-    "esp_diag_scan": [P, P, P, P, c_float, P, P, P, c_longlong, P, P, P, c_int, c_int, c_int, c_int, P],
+    "esp_diag_scan": [P, P, P, P, c_float, P, P, P, c_longlong, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
     "esp_router_topk": [P, c_int, P, P, c_int, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "esp_moe_permute": [P, P, c_int, c_int, c_int, P, P, P, P, P, P, P, P, c_int, c_int, P, P, P],
     "esp_gather_rows": [P, P, P, c_int, c_int, P],
@@ -75,10 +75,10 @@ _SIGNATURES = {
                             c_int, c_int, c_int, P, P],
     "esp_attn_prefill": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                          c_int, P, P],
-    "esp_attn_prefill_tc05": [P, c_longlong, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                              P, P],
+    "esp_attn_prefill_tc05": [P, c_longlong, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                              c_int, c_int, P, P],
     "esp_attn_decode": [P, P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                        c_int, P, P],
+                        c_int, c_float, c_int, P, P],
 }
 
 _bound: dict = {}
@@ -457,14 +457,17 @@ def skinny_fits(k: int) -> bool:
 
 
 def gemm_skinny(a, w, c, swiglu=False, row_scale=None, a_rows=None, group_offsets=None, rows=None, max_rows=None,
-                offsets_ready=False, xielu_pq=None):
+                offsets_ready=False, xielu_pq=None, relu2=False):
     """Weight-streaming product for few rows; bfloat16 a and w.  Plain: c[m] =
     scale[m] * a[row(m)] @ w[g].T with w [N,K] or [G,N,K].  swiglu: w holds
     [gate rows; up rows] ([2I,K] or [G,2I,K]) and c[m, j] = silu(gate_j) * up_j
     ([rows, I]).  ``max_rows``: upper bound of the rows of one group.  ``offsets_ready``: the group offsets (and
     ``row_scale``) were complete before the kernel that runs right before this one started, so this one may
     find its group and ask for its weights while that kernel still runs (only ``a`` is waited for).  ``xielu_pq`` (plain
-    form; float32 [2] on the device): every output passes through the xIELU with these two raw numbers."""
+    form; float32 [2] on the device): every output passes through the xIELU with these two raw numbers.  ``relu2`` (plain
+    form): every output, after its row's scale, becomes max(v, 0)^2."""
+    if relu2 and (swiglu or xielu_pq is not None):
+        raise Backend("gemm_skinny: one activation at a time")
     grouped = group_offsets is not None
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise Backend("gemm_skinny takes bfloat16 operands")
@@ -484,7 +487,7 @@ def gemm_skinny(a, w, c, swiglu=False, row_scale=None, a_rows=None, group_offset
     code = _fn("bf16", "esp_gemm_skinny")(
         a.data_ptr(), a.stride(0), _ptr(a_rows, torch.int32, "a_rows"), w.data_ptr(), wn * k,
         _ptr(row_scale, torch.float32, "row_scale"), c.data_ptr(), _is_bf16(c), c.stride(0),
-        _ptr(group_offsets, torch.int32, "group_offsets"), groups, m, n, k, max_rows, 1 if swiglu else 0,
+        _ptr(group_offsets, torch.int32, "group_offsets"), groups, m, n, k, max_rows, 2 if relu2 else 1 if swiglu else 0,
         1 if offsets_ready else 0, _ptr(xielu_pq, torch.float32, "xielu_pq"), _stream())
     _check(code, "gemm_skinny")
 
@@ -549,13 +552,14 @@ ATTN_DECODE_COUNTERS = 65536
 
 
 def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, tok_pos, block_table, page, nh, nkv, hd,
-                window, split, n_splits, status, seq_past=None):
+                window, split, n_splits, status, seq_past=None, scale=0.0, sink=False):
     """Split-key attention for few token rows (bfloat16; head sizes 64, 128, 192, 256).  ``split``: key
     positions per block (a multiple of 64); n_splits >= ceil(positions / split).  part_o float32
     [N, nh, n_splits, hd] and part_ml float32 [N, nh, n_splits, 2] are scratch; ``counters``: int32, at least
     N * nh words, all zero (the kernel leaves them zero).  ``seq_past`` (int32 per sequence of the step: the
     positions cached before it): blocks whose keys are all older then load them without waiting for the
-    kernel before this one, which writes the step's new keys and values."""
+    kernel before this one, which writes the step's new keys and values.  ``scale`` > 0 multiplies the scores instead
+    of the division by sqrt(hd); ``sink``: the softmax's denominator holds one more term exp(0)."""
     if counters.numel() < q.shape[0] * nh:
         raise Backend("attn_decode: too few counters for this many rows and heads")
     if split < 64 or split % 64:
@@ -570,8 +574,8 @@ def attn_decode(q, k_cache, v_cache, out, part_o, part_ml, counters, tok_seq, to
         _ptr(out, torch.bfloat16), _ptr(part_o, torch.float32), _ptr(part_ml, torch.float32),
         _ptr(counters, torch.int32), _ptr(tok_seq, torch.int32), _ptr(tok_pos, torch.int32), _ptr(seq_past, torch.int32),
         _ptr(block_table, torch.int32), block_table.shape[1],
-        k_cache.shape[0], page, n, nh, nkv, hd, int(window or 0), split, n_splits, _ptr(status, torch.int32),
-        _stream()), "attn_decode")
+        k_cache.shape[0], page, n, nh, nkv, hd, int(window or 0), split, n_splits, float(scale), 1 if sink else 0,
+        _ptr(status, torch.int32), _stream()), "attn_decode")
 
 
 def attn_flash_fits(hd, vd=None, page=64) -> bool:
@@ -606,11 +610,12 @@ def attn_prefill_tc05_fits(hd, page) -> bool:
 
 
 def attn_prefill_tc05(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start, seq_past, block_table, page, nh, nkv, hd,
-                      window, status):
+                      window, status, scale=0.0, sink=False):
     """Prefill attention on tcgen05 with accumulators in tensor memory (bfloat16; head size 64 or 128; pages
     of 64 positions).  Same arguments as attn_prefill, but tile_seq / tile_first list tiles of
     ATTN_TC05_TILE_ROWS new tokens, best with the tiles that see the most keys first (the order only matters
-    for the balance)."""
+    for the balance).  ``scale`` > 0 multiplies the scores instead of the division by sqrt(hd); ``sink``: the softmax's
+    denominator holds one more term exp(0)."""
     if not attn_prefill_tc05_fits(hd, page):
         raise Backend(f"attn_prefill_tc05: head size {hd} / page {page} not taken (64 or 128; page 64)")
     if not q.is_contiguous() or q.numel() != q.shape[0] * nh * hd:
@@ -619,8 +624,8 @@ def attn_prefill_tc05(q, k_cache, v_cache, out, tile_seq, tile_first, seq_start,
         _ptr(q, torch.bfloat16, "q"), q.shape[0], _ptr(k_cache, torch.bfloat16), _ptr(v_cache, torch.bfloat16),
         _ptr(out, torch.bfloat16), _ptr(tile_seq, torch.int32), _ptr(tile_first, torch.int32),
         _ptr(seq_start, torch.int32), _ptr(seq_past, torch.int32), _ptr(block_table, torch.int32),
-        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, int(window or 0),
-        _ptr(status, torch.int32), _stream()), "attn_prefill_tc05")
+        block_table.shape[1], k_cache.shape[0], page, tile_seq.shape[0], nh, nkv, hd, float(scale), 1 if sink else 0,
+        int(window or 0), _ptr(status, torch.int32), _stream()), "attn_prefill_tc05")
 
 
 def gather_rows(src, rows, out):
@@ -724,6 +729,7 @@ def token_shift_keep(h, prev_state, seq_start, seq_slot, n_seqs: int):
 
 SCAN_DECAY_BONUS = 0          # d = exp(-exp(g + bias)), the current token weighted by ``bonus``, output before the update
 SCAN_LOWER_SIGMOID = 1        # d = lower + (1 - lower) sigmoid(g + bias), k = 1 - d, q = silu(q), output after the update
+SCAN_SCALAR_DECAY = 2         # with ready=True: g holds one ready-made decay per head and token [rows, heads]; output after the update
 SCAN_MAX_KEY_DIM = 256
 
 
@@ -913,33 +919,36 @@ def qknorm_kvwrite(qkv, bias, q_w, k_w, eps, temp_coef, temp_every, tok_seq, tok
 # ---------------------------------------------------------------------------
 # matrix memory and gated diagonal recurrence (library ``mixers``)
 
-def matrix_memory_prepare(q, k, v, gi, gf, ld, bias_i, bias_f, cap, q_scale, m_state, seq_start, seq_slot, q_out, k_out,
-                          d_out, v_out, m_out, n_seqs, heads, key_dim, value_dim, value_cols):
-    """Gates of a matrix memory with exponential gating and what ``gated_scan(SCAN_LOWER_SIGMOID, ready=True)`` reads:
-    q, k, v, gi, gf are views into one float32 projection with row stride ``ld``; m_state float32 [slots, heads] (a
-    view with its slot stride); outputs float32: q_out, k_out, d_out [N, heads*key_dim], v_out [N, heads*value_cols]
-    (column value_dim is one, later ones zero), m_out [N, heads]."""
-    for t in (q, k, v, gi, gf):
+def matrix_memory_prepare(v, gi, gf, ld, bias_i, bias_f, cap, m_state, seq_start, seq_slot, v_out, keep_take_m, n_seqs, heads,
+                          value_dim, value_cols):
+    """Gates of a matrix memory with exponential gating: v, gi, gf are views into one float32 projection with row
+    stride ``ld``; m_state float32 [slots, heads] (a view with its slot stride).  keep_take_m float32 [3, N, heads]
+    receives the decay exp(f + m' - m), the input weight exp(i - m) and the running maximum m of every token and head
+    (``gated_scan(SCAN_SCALAR_DECAY, ...)`` takes the first as its decays, ``matrix_memory_finish`` reads the last);
+    v_out float32 [N, heads * value_cols] = input weight * [v, 1, 0 ...]."""
+    for t in (v, gi, gf):
         if t.dtype != torch.float32 or t.stride(-1) != 1 or t.stride(0) != ld:
             raise Backend("matrix_memory_prepare: the projections must be float32 views of rows with stride ld")
+    if tuple(keep_take_m.shape) != (3, v.shape[0], heads):
+        raise Backend("matrix_memory_prepare: keep_take_m must be [3, rows, heads]")
     _check(_fn("mixers", "esp_matrix_memory_prepare")(
-        q.data_ptr(), k.data_ptr(), v.data_ptr(), gi.data_ptr(), gf.data_ptr(), int(ld), _ptr(bias_i, torch.float32),
-        _ptr(bias_f, torch.float32), float(cap), float(q_scale), m_state.data_ptr(), m_state.stride(0),
-        _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(q_out, torch.float32), _ptr(k_out, torch.float32),
-        _ptr(d_out, torch.float32), _ptr(v_out, torch.float32), _ptr(m_out, torch.float32), n_seqs, heads, key_dim,
-        value_dim, value_cols, _stream()), "matrix_memory_prepare")
+        v.data_ptr(), gi.data_ptr(), gf.data_ptr(), int(ld), _ptr(bias_i, torch.float32), _ptr(bias_f, torch.float32),
+        float(cap), m_state.data_ptr(), m_state.stride(0), _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32),
+        _ptr(v_out, torch.float32), _ptr(keep_take_m, torch.float32), v.shape[0], n_seqs, heads, value_dim, value_cols,
+        _stream()), "matrix_memory_prepare")
 
 
-def matrix_memory_finish(o, m, w, gate, y, heads, value_dim, value_cols, eps, floor_eps):
-    """y[n, h, :] = unit-rms(o[n, h, :value_dim] / (max(|o[n, h, value_dim]|, exp(-m[n, h])) + floor_eps)) * w[h] *
-    sigmoid(gate[n, h, :]); o float32 [N, heads*value_cols], gate a float32 view [N, heads*value_dim] or None."""
+def matrix_memory_finish(o, m, w, gate, y, heads, value_dim, value_cols, eps, floor_eps, q_scale=1.0):
+    """y[n, h, :] = unit-rms(q_scale o[n, h, :value_dim] / (max(|q_scale o[n, h, value_dim]|, exp(-m[n, h])) + floor_eps))
+    * w[h] * sigmoid(gate[n, h, :]); o float32 [N, heads*value_cols], gate a float32 view [N, heads*value_dim] or None."""
     n = o.shape[0]
     if gate is not None and (gate.dtype != torch.float32 or gate.stride(-1) != 1):
         raise Backend("matrix_memory_finish: the gate must be a float32 view with unit column stride")
     _check(_fn("mixers", "esp_matrix_memory_finish")(
         _ptr(o, torch.float32, "o"), _ptr(m, torch.float32, "m"), _ptr(w, torch.float32, "w"),
         gate.data_ptr() if gate is not None else None, gate.stride(0) if gate is not None else 0, _ptr(y, FLOATS, "y"),
-        _is_bf16(y), n, heads, value_dim, value_cols, float(eps), float(floor_eps), _stream()), "matrix_memory_finish")
+        _is_bf16(y), n, heads, value_dim, value_cols, float(eps), float(floor_eps), float(q_scale), _stream()),
+        "matrix_memory_finish")
 
 
 CONV_MAX_TAPS = 16
@@ -963,10 +972,10 @@ def conv_branches(proj, bias_y, bias_x, conv_w, conv_b, conv_state, tok_seq, seq
 
 def diag_scan(gates, bias_r, bias_i, lam, decay_scale, u, gate, state, seq_start, seq_slot, out, n_seqs, channels, blocks):
     """S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t, a_t = exp(-decay_scale sigmoid(raw_r + bias_r) softplus(lam)),
-    i_t = sigmoid(raw_i + bias_i); out = S_t * gate.  gates float32 [N, blocks, 2, C / blocks]; state float32 [slots, C]
-    (a view with its slot stride)."""
+    i_t = sigmoid(raw_i + bias_i); out = S_t * gate.  gates float32 [N, blocks, 2, C / blocks] (overwritten with the
+    recurrence's coefficients); state float32 [slots, C] (a view with its slot stride)."""
     _check(_fn("mixers", "esp_diag_scan")(
         _ptr(gates, torch.float32, "gates"), _ptr(bias_r, torch.float32), _ptr(bias_i, torch.float32),
         _ptr(lam, torch.float32), float(decay_scale), _ptr(u, torch.float32), _ptr(gate, torch.float32), state.data_ptr(),
         state.stride(0), _ptr(seq_start, torch.int32), _ptr(seq_slot, torch.int32), _ptr(out, FLOATS), _is_bf16(out),
-        n_seqs, channels, blocks, _stream()), "diag_scan")
+        gates.shape[0], n_seqs, channels, blocks, _stream()), "diag_scan")

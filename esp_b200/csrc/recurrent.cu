@@ -113,8 +113,9 @@ constexpr int CHUNK = 16;       // tokens staged at a time
 constexpr int MAX_K = 16 * KT;  // key channels of a head that the kernel takes
 
 enum : int {
-    GATE_EXP_EXP = 0,      // d = exp(-exp(g + bias));  k, q as given;  o reads S_(t-1) + diag(bonus) k v^T
-    GATE_LOWER_SIGMOID = 1 // d = lower + (1 - lower) * sigmoid(g + bias);  k = 1 - d;  q = silu(q);  o reads S_t
+    GATE_EXP_EXP = 0,       // d = exp(-exp(g + bias));  k, q as given;  o reads S_(t-1) + diag(bonus) k v^T
+    GATE_LOWER_SIGMOID = 1, // d = lower + (1 - lower) * sigmoid(g + bias);  k = 1 - d;  q = silu(q);  o reads S_t
+    GATE_SCALAR = 2         // d is one number per head and token, ready made (g: [rows, H]);  k, q as given;  o reads S_t
 };
 
 // The gates, written with explicit operations so that the kernel that makes them ahead of the recurrence and the
@@ -182,9 +183,10 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
         for (int i = 0; i < KT; i++) S[j][i] = (live[j] && part * KT + i < K) ? srow[(size_t)j * K + i] : 0.f;
 
     // 16-byte copies where every row piece is aligned (the usual case: K, V and the row strides multiples of 4)
-    const bool wide = (K % 4 == 0) && (V % 4 == 0) && (vt % 4 == 0) && (ldq % 4 == 0) && (ldg % 4 == 0) && (ldv % 4 == 0) &&
-                      (!(MODE == GATE_EXP_EXP || READY) || ldk % 4 == 0) &&
-                      ((((size_t)q | (size_t)g | (size_t)v | (size_t)((MODE == GATE_EXP_EXP || READY) ? k : q)) & 15) == 0);
+    const bool wide = (K % 4 == 0) && (V % 4 == 0) && (vt % 4 == 0) && (ldq % 4 == 0) && (MODE == GATE_SCALAR || ldg % 4 == 0) &&
+                      (ldv % 4 == 0) && (!(MODE == GATE_EXP_EXP || READY) || ldk % 4 == 0) &&
+                      ((((size_t)q | (size_t)(MODE == GATE_SCALAR ? q : g) | (size_t)v |
+                         (size_t)((MODE == GATE_EXP_EXP || READY) ? k : q)) & 15) == 0);
     float bonus_r[KT];
 #pragma unroll
     for (int i = 0; i < KT; i++) bonus_r[i] = c_bonus[part * KT + i];
@@ -198,7 +200,7 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
                 const size_t r = (size_t)(r0 + t);
                 cp_async16(base + t * kp + at(c), q + r * ldq + h * K + c);
                 if (MODE == GATE_EXP_EXP || READY) cp_async16(base + (CHUNK + t) * kp + at(c), k + r * ldk + h * K + c);
-                cp_async16(base + (2 * CHUNK + t) * kp + at(c), g + r * ldg + h * K + c);
+                if (MODE != GATE_SCALAR) cp_async16(base + (2 * CHUNK + t) * kp + at(c), g + r * ldg + h * K + c);
             }
             for (int i = tid; i < count * v4; i += nthreads) {
                 const int t = i / v4, c = (i - t * v4) * 4;
@@ -210,13 +212,15 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
                 const size_t r = (size_t)(r0 + t);
                 cp_async4(base + t * kp + at(c), q + r * ldq + h * K + c);
                 if (MODE == GATE_EXP_EXP || READY) cp_async4(base + (CHUNK + t) * kp + at(c), k + r * ldk + h * K + c);
-                cp_async4(base + (2 * CHUNK + t) * kp + at(c), g + r * ldg + h * K + c);
+                if (MODE != GATE_SCALAR) cp_async4(base + (2 * CHUNK + t) * kp + at(c), g + r * ldg + h * K + c);
             }
             for (int i = tid; i < count * vt; i += nthreads) {
                 const int t = i / vt, c = i - t * vt;
                 if (v0 + c < V) cp_async4(base + 3 * CHUNK * kp + t * vt + c, v + (size_t)(r0 + t) * ldv + h * V + v0 + c);
             }
         }
+        if (MODE == GATE_SCALAR && tid < count)          // the token's one decay, at the head of its row of d
+            cp_async4(base + (2 * CHUNK + tid) * kp, g + (size_t)(r0 + tid) * ldg + h);
         cp_async_commit();
     };
 
@@ -251,6 +255,7 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
             const float4* tk = reinterpret_cast<const float4*>(sk + t * kp + part * KTP);
             const float4* td = reinterpret_cast<const float4*>(sd + t * kp + part * KTP);
             float vv[CPT], oe[CPT][4];
+            const float d_all = MODE == GATE_SCALAR ? sd[t * kp] : 0.f;
 #pragma unroll
             for (int j = 0; j < CPT; j++) {
                 vv[j] = live[j] ? sv[t * vt + col + j] : 0.f;
@@ -258,7 +263,7 @@ gated_scan_kernel(const float* __restrict__ q, long long ldq, const float* __res
             }
 #pragma unroll
             for (int i4 = 0; i4 < KT / 4; i4++) {
-                const float4 q4 = tq[i4], k4 = tk[i4], d4 = td[i4];
+                const float4 q4 = tq[i4], k4 = tk[i4], d4 = MODE == GATE_SCALAR ? make_float4(d_all, d_all, d_all, d_all) : td[i4];
                 const float qe[4] = {q4.x, q4.y, q4.z, q4.w}, ke[4] = {k4.x, k4.y, k4.z, k4.w}, de[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
@@ -372,27 +377,27 @@ __global__ void head_rmsnorm_gate_kernel(const float* __restrict__ o, const floa
 // The gates of a matrix memory with exponential gating, ahead of esp_gated_scan(mode 1, ready): per head and token
 //     i = cap tanh((raw_i + b_i) / cap),  f = logsigmoid(cap tanh((raw_f + b_f) / cap)),
 //     m_t = max(f + m_(t-1), i),  keep = exp(f + m_(t-1) - m_t),  take = exp(i - m_t)
-// and from them what the recurrence reads: q_out = q * q_scale, k_out = take * k, d_out = keep on every key channel,
-// v_out = [v, 1, 0 ...] (V1 >= V + 1 columns a head: column V accumulates the normaliser n_t = keep n_(t-1) + take k_t as
-// one more value column of the same recurrence; further columns are zero and only align the rows), m_out = m_t.  m_(t-1) of a run's first token is the sequence's state
-// (m_state[slot * state_stride + h], zero in a fresh slot), which the run's last m_t replaces.  A block owns
-// (sequence, head); the gates of 128 tokens are made in parallel, one thread then walks the chain of maxima (an add
-// and a max per token, in token order, so cutting a sequence into steps changes no bit), and all write the rows.
+// First kernel: a block owns (sequence, head); the gates of 128 tokens are made in parallel, one thread then walks the
+// chain of maxima (an add and a max per token, in token order, so cutting a sequence into steps changes no bit), and
+// keep, take and m go out as [rows, H].  m_(t-1) of a run's first token is the sequence's state (m_state[slot *
+// state_stride + h], zero in a fresh slot), which the run's last m_t replaces.
+// Second kernel, over all rows at once: the values the recurrence reads, v_out = take * [v, 1, 0 ...] (V1 >= V + 1
+// columns a head: the input weight rides on the values, so that the keys go in as projected; column V accumulates the
+// normaliser n_t = keep n_(t-1) + take k_t as one more value column of the same recurrence; further columns are zero
+// and only align the rows).  The recurrence takes keep as its one decay per head and token (mode 2).
 constexpr int MM_CHUNK = 128;
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 __global__ void __launch_bounds__(MM_CHUNK)
-matrix_memory_prepare_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                             const float* __restrict__ gi, const float* __restrict__ gf, long long ld,
-                             const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap, float q_scale,
-                             float* __restrict__ m_state, long long state_stride, const int* __restrict__ seq_start,
-                             const int* __restrict__ seq_slot, float* __restrict__ q_out, float* __restrict__ k_out,
-                             float* __restrict__ d_out, float* __restrict__ v_out, float* __restrict__ m_out, int H, int K,
-                             int V, int V1) {
+matrix_memory_gates_kernel(const float* __restrict__ gi, const float* __restrict__ gf, long long ld,
+                           const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap,
+                           float* __restrict__ m_state, long long state_stride, const int* __restrict__ seq_start,
+                           const int* __restrict__ seq_slot, float* __restrict__ keep_out, float* __restrict__ take_out,
+                           float* __restrict__ m_out, int H) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float s_i[MM_CHUNK], s_f[MM_CHUNK], s_keep[MM_CHUNK], s_take[MM_CHUNK];
+    __shared__ float s_i[MM_CHUNK], s_f[MM_CHUNK], s_carried[MM_CHUNK], s_new[MM_CHUNK];
     __shared__ float s_m;
     const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int row0 = seq_start[b], row1 = seq_start[b + 1];
@@ -411,56 +416,80 @@ matrix_memory_prepare_kernel(const float* __restrict__ q, const float* __restric
         __syncthreads();
         if (tid == 0) {
             float m = s_m;
+#pragma unroll 8
             for (int t = 0; t < count; t++) {
                 const float carried = __fadd_rn(s_f[t], m);
-                const float m_new = fmaxf(carried, s_i[t]);
-                s_keep[t] = carried;                 // turned into exp(carried - m_new) below, in parallel
-                s_take[t] = m_new;
-                m = m_new;
+                m = fmaxf(carried, s_i[t]);
+                s_carried[t] = carried;
+                s_new[t] = m;
             }
             s_m = m;
         }
         __syncthreads();
         if (tid < count) {
-            const float m_new = s_take[tid];
-            m_out[(size_t)(r0 + tid) * H + h] = m_new;
-            s_keep[tid] = expf(s_keep[tid] - m_new);
-            s_take[tid] = expf(s_i[tid] - m_new);
-        }
-        __syncthreads();
-        for (int idx = tid; idx < count * K; idx += MM_CHUNK) {
-            const int t = idx / K, c = idx - t * K;
-            const size_t r = (size_t)(r0 + t);
-            const size_t o = (r * H + h) * K + c;
-            q_out[o] = q[r * ld + h * K + c] * q_scale;
-            k_out[o] = k[r * ld + h * K + c] * s_take[t];
-            d_out[o] = s_keep[t];
-        }
-        for (int idx = tid; idx < count * V1; idx += MM_CHUNK) {
-            const int t = idx / V1, c = idx - t * V1;
-            const size_t r = (size_t)(r0 + t);
-            v_out[(r * H + h) * V1 + c] = c < V ? v[r * ld + h * V + c] : (c == V ? 1.0f : 0.f);
+            const size_t o = (size_t)(r0 + tid) * H + h;
+            const float m_new = s_new[tid];
+            m_out[o] = m_new;
+            keep_out[o] = expf(s_carried[tid] - m_new);
+            take_out[o] = expf(s_i[tid] - m_new);
         }
     }
     __syncthreads();
     if (tid == 0) *mp = s_m;
 }
 
-// What follows the recurrence (o has V1 columns a head): o[n, h, :V] / (max(|o[n, h, V]|, exp(-m[n, h])) + floor_eps), each head scaled to unit
+__global__ void matrix_memory_expand_kernel(const float* __restrict__ v, long long ld, const float* __restrict__ take,
+                                            float* __restrict__ v_out, int H, int V, int V1) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t r = blockIdx.x;
+    const int vw = H * V1;
+    for (int c = threadIdx.x; c < vw; c += blockDim.x) {
+        const int h = c / V1, j = c - h * V1;
+        const float w = take[r * H + h];
+        v_out[r * vw + c] = j < V ? v[r * ld + h * V + j] * w : (j == V ? w : 0.f);
+    }
+}
+
+// What follows the recurrence (o has V1 columns a head; the queries went in unscaled, so o is multiplied by q_scale
+// first): o[n, h, :V] / (max(|o[n, h, V]|, exp(-m[n, h])) + floor_eps), each head scaled to unit
 // root mean square (eps inside the root), times a weight per channel, times sigmoid(gate).  One warp per (row, head).
 template <typename T>
 __global__ void matrix_memory_finish_kernel(const float* __restrict__ o, const float* __restrict__ m,
                                             const float* __restrict__ w, const float* __restrict__ gate, long long ldgate,
                                             T* __restrict__ y, int n_rows, int H, int V, int V1, float eps,
-                                            float floor_eps) {
+                                            float floor_eps, float q_scale) {
     pdl_trigger();
     pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= n_rows * H) return;
     const int n = warp / H, h = warp - n * H;
     const float* src = o + ((size_t)n * H + h) * V1;
-    const float den = fmaxf(fabsf(src[V]), expf(-m[(size_t)n * H + h])) + floor_eps;
+    const float den = (fmaxf(fabsf(src[V] * q_scale), expf(-m[(size_t)n * H + h])) + floor_eps) / q_scale;
     float ss = 0.f;
+    if (V <= 512) {
+        // the head's values stay in registers: all loads in flight at once, one pass over memory
+        float val[16], gz[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const int i = lane + 32 * j;
+            val[j] = i < V ? src[i] / den : 0.f;
+            gz[j] = (gate && i < V) ? gate[(size_t)n * ldgate + h * V + i] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++) ss = fmaf(val[j], val[j], ss);      // lane-wise in index order, as the loop below
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const int i = lane + 32 * j;
+            if (i >= V) break;
+            float r = val[j] * inv * w[h * V + i];
+            if (gate) r *= 1.0f / (1.0f + expf(-gz[j]));
+            y[((size_t)n * H + h) * V + i] = from_f32<T>(r);
+        }
+        return;
+    }
     for (int i = lane; i < V; i += 32) {
         const float val = src[i] / den;
         ss = fmaf(val, val, ss);
@@ -540,39 +569,79 @@ __global__ void conv_state_keep_kernel(const float* __restrict__ proj, const flo
 
 // S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t with a_t = exp(-decay_scale r_t softplus(lam)), r_t = sigmoid(raw_r + b_r),
 // i_t = sigmoid(raw_i + b_i); out = S_t * gate.  gates: [rows, blocks, 2, C / blocks] float (a block's r then its i, as the
-// block-diagonal projection leaves them).  S lives in state[slot * state_stride + c], 32-bit.  A thread owns (sequence,
-// channel) and walks the run's tokens in order; 1 - a^2 is taken as -expm1(2 ln a).
-template <typename T>
-__global__ void __launch_bounds__(128)
-diag_scan_kernel(const float* __restrict__ gates, const float* __restrict__ bias_r, const float* __restrict__ bias_i,
-                 const float* __restrict__ lam, float decay_scale, const float* __restrict__ u, const float* __restrict__ gate,
-                 float* __restrict__ state, long long state_stride, const int* __restrict__ seq_start,
-                 const int* __restrict__ seq_slot, T* __restrict__ out, int C, int cb) {
+// block-diagonal projection leaves them).  Two kernels.  The first, over all rows at once, turns the raw gates into the
+// recurrence's two coefficients in place: a_t where r was, sqrt(1 - a_t^2) i_t u_t where i was (1 - a^2 is taken as
+// -expm1(2 ln a)).  The second is the chain itself: a thread owns (sequence, channel) and walks the run's tokens in
+// order, one multiply-add a token.  A block owns 32 channels of a sequence: all its warps stage the coefficients of
+// DIAG_TILE tokens at a time into one of two shared-memory buffers by cp.async, the next tile while the first warp
+// walks the chain over this one, so the chain never waits for global memory.  S lives in state[slot * state_stride
+// + c], 32-bit.
+constexpr int DIAG_TILE = 64, DIAG_THREADS = 128;
+
+__global__ void diag_coefficients_kernel(float* __restrict__ gates, const float* __restrict__ bias_r,
+                                         const float* __restrict__ bias_i, const float* __restrict__ lam, float decay_scale,
+                                         const float* __restrict__ u, int C, int cb) {
     pdl_trigger();
     pdl_wait();
-    const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
-    if (c >= C) return;
+    const size_t r = blockIdx.x;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const int blk = c / cb, j = c - blk * cb;
+        float* g = gates + r * 2 * C + (size_t)blk * 2 * cb + j;
+        const float l = lam[c];
+        const float rate = decay_scale * (l > 20.f ? l : log1pf(expf(l)));
+        const float rr = 1.0f / (1.0f + expf(-(g[0] + (bias_r ? bias_r[c] : 0.f))));
+        const float ii = 1.0f / (1.0f + expf(-(g[cb] + (bias_i ? bias_i[c] : 0.f))));
+        const float log_a = -rate * rr;
+        g[0] = expf(log_a);
+        g[cb] = sqrtf(-expm1f(2.0f * log_a)) * (ii * u[r * C + c]);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(DIAG_THREADS)
+diag_scan_kernel(const float* __restrict__ coef, const float* __restrict__ gate, float* __restrict__ state,
+                 long long state_stride, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                 T* __restrict__ out, int C, int cb) {
+    pdl_trigger();
+    __shared__ float buf[2][3][DIAG_TILE][32];          // a_t, the input term, the gate branch: two tiles of tokens
+    const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+    const int c = blockIdx.y * 32 + lane;
+    const bool live = c < C;
     const int row0 = seq_start[b], row1 = seq_start[b + 1];
     if (row1 <= row0) return;
-    const int blk = c / cb, j = c - blk * cb;
+    const int blk = live ? c / cb : 0, j = live ? c - blk * cb : 0;
     const size_t goff = (size_t)blk * 2 * cb + j;
-    const float br = bias_r ? bias_r[c] : 0.f, bi = bias_i ? bias_i[c] : 0.f;
-    const float l = lam[c];
-    const float rate = decay_scale * (l > 20.f ? l : log1pf(expf(l)));
+    pdl_wait();
+    auto stage = [&](int which, int r0) {
+        const int count = min(DIAG_TILE, row1 - r0);
+        if (live) {
+            for (int t = tid >> 5; t < count; t += DIAG_THREADS / 32) {
+                const float* g = coef + (size_t)(r0 + t) * 2 * C + goff;
+                cp_async4(&buf[which][0][t][lane], g);
+                cp_async4(&buf[which][1][t][lane], g + cb);
+                cp_async4(&buf[which][2][t][lane], gate + (size_t)(r0 + t) * C + c);
+            }
+        }
+        cp_async_commit();
+    };
     float* sp = state + (size_t)seq_slot[b] * state_stride + c;
-    float S = *sp;
-#pragma unroll 4
-    for (int r = row0; r < row1; r++) {
-        const float* g = gates + (size_t)r * 2 * C + goff;
-        const float rr = 1.0f / (1.0f + expf(-(g[0] + br)));
-        const float ii = 1.0f / (1.0f + expf(-(g[cb] + bi)));
-        const float log_a = -rate * rr;
-        const float a = expf(log_a);
-        const float in = sqrtf(-expm1f(2.0f * log_a)) * (ii * u[(size_t)r * C + c]);
-        S = fmaf(a, S, in);
-        out[(size_t)r * C + c] = from_f32<T>(S * gate[(size_t)r * C + c]);
+    float S = (live && tid < 32) ? *sp : 0.f;
+    stage(0, row0);
+    int which = 0;
+    for (int r0 = row0; r0 < row1; r0 += DIAG_TILE, which ^= 1) {
+        const int count = min(DIAG_TILE, row1 - r0);
+        cp_async_wait_all();
+        __syncthreads();                                 // the tile has landed; the chain is done with the other one
+        if (r0 + DIAG_TILE < row1) stage(which ^ 1, r0 + DIAG_TILE);
+        if (tid < 32 && live) {
+#pragma unroll 8
+            for (int t = 0; t < count; t++) {
+                S = fmaf(buf[which][0][t][lane], S, buf[which][1][t][lane]);
+                out[(size_t)(r0 + t) * C + c] = from_f32<T>(S * buf[which][2][t][lane]);
+            }
+        }
     }
-    *sp = S;
+    if (tid < 32 && live) *sp = S;
 }
 }  // namespace
 
@@ -621,7 +690,8 @@ ESP_API int esp_gate_prepare(int mode, const float* q, long long ldq, const floa
     return esp_launch_status();
 }
 
-// mode: 0 = decay exp(-exp(.)) with an extra weight on the token being read, 1 = lower-bounded sigmoid gate that also writes.
+// mode: 0 = decay exp(-exp(.)) with an extra weight on the token being read, 1 = lower-bounded sigmoid gate that also writes,
+// 2 (with ready) = one ready-made decay per head and token, g being [rows, H]; q and k as given, the output reads S_t.
 // ready: q, k and g already hold the query, the written key and the decay (esp_gate_prepare made them).
 ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, const float* k, long long ldk, const float* g,
                            long long ldg, const float* v, long long ldv, const float* gate_bias, const float* lower,
@@ -649,7 +719,8 @@ ESP_API int esp_gated_scan(int mode, int ready, const float* q, long long ldq, c
         esp_launch_pdl(READY_ ? 0 : ESP_PDL_SMALL, kernel, grid, dim3(threads), smem, stream, q, ldq, k, ldk, g, ldg, v, ldv, \
                        gate_bias, lower, bonus, state, state_stride, seq_start, seq_slot, out, H, K, V, ks, vt);            \
     }
-    if (mode == GATE_EXP_EXP && !ready) ESP_SCAN(GATE_EXP_EXP, false)
+    if (mode == GATE_SCALAR && ready) ESP_SCAN(GATE_SCALAR, true)
+    else if (mode == GATE_EXP_EXP && !ready) ESP_SCAN(GATE_EXP_EXP, false)
     else if (mode == GATE_EXP_EXP) ESP_SCAN(GATE_EXP_EXP, true)
     else if (mode == GATE_LOWER_SIGMOID && !ready) ESP_SCAN(GATE_LOWER_SIGMOID, false)
     else if (mode == GATE_LOWER_SIGMOID) ESP_SCAN(GATE_LOWER_SIGMOID, true)
@@ -672,31 +743,36 @@ ESP_API int esp_head_rmsnorm_gate(const float* o, const float* w, int w_head_str
     return esp_launch_status();
 }
 
-ESP_API int esp_matrix_memory_prepare(const float* q, const float* k, const float* v, const float* gi, const float* gf,
-                                      long long ld, const float* bias_i, const float* bias_f, float cap, float q_scale,
-                                      float* m_state, long long state_stride, const int* seq_start, const int* seq_slot,
-                                      float* q_out, float* k_out, float* d_out, float* v_out, float* m_out, int n_seqs, int H,
-                                      int K, int V, int V1, cudaStream_t stream) {
-    if (n_seqs <= 0) return 0;
-    if (H <= 0 || H > 65535 || K <= 0 || V <= 0 || V1 <= V || !(cap > 0.f)) return (int)cudaErrorInvalidValue;
-    esp_launch_pdl(ESP_PDL_SMALL, matrix_memory_prepare_kernel, dim3(n_seqs, H), dim3(MM_CHUNK), 0, stream, q, k, v, gi, gf, ld,
-                   bias_i, bias_f, cap, q_scale, m_state, state_stride, seq_start, seq_slot, q_out, k_out, d_out, v_out, m_out,
-                   H, K, V, V1);
+// keep_take_m: 3 * rows * H floats: the decay (what esp_gated_scan mode 2 takes as g), the input weight and m_t (which
+// esp_matrix_memory_finish reads) of every token and head.
+ESP_API int esp_matrix_memory_prepare(const float* v, const float* gi, const float* gf, long long ld, const float* bias_i,
+                                      const float* bias_f, float cap, float* m_state, long long state_stride,
+                                      const int* seq_start, const int* seq_slot, float* v_out, float* keep_take_m, int n_rows,
+                                      int n_seqs, int H, int V, int V1, cudaStream_t stream) {
+    if (n_seqs <= 0 || n_rows <= 0) return 0;
+    if (H <= 0 || H > 65535 || V <= 0 || V1 <= V || !(cap > 0.f)) return (int)cudaErrorInvalidValue;
+    float* keep = keep_take_m;
+    float* take = keep + (size_t)n_rows * H;
+    float* m_out = take + (size_t)n_rows * H;
+    esp_launch_pdl(ESP_PDL_SMALL, matrix_memory_gates_kernel, dim3(n_seqs, H), dim3(MM_CHUNK), 0, stream, gi, gf, ld, bias_i,
+                   bias_f, cap, m_state, state_stride, seq_start, seq_slot, keep, take, m_out, H);
+    esp_launch_pdl(ESP_PDL_SMALL, matrix_memory_expand_kernel, dim3(n_rows), dim3(256), 0, stream, v, ld, (const float*)take,
+                   v_out, H, V, V1);
     return esp_launch_status();
 }
 
 ESP_API int esp_matrix_memory_finish(const float* o, const float* m, const float* w, const float* gate, long long ldgate,
                                      void* y, int y_is_bf16, int n_rows, int H, int V, int V1, float eps, float floor_eps,
-                                     cudaStream_t stream) {
+                                     float q_scale, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const long long warps = (long long)n_rows * H;
     const int blocks = (int)((warps + 7) / 8);
     if (y_is_bf16)
         esp_launch_pdl(ESP_PDL_SMALL, matrix_memory_finish_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, o, m, w, gate,
-                       ldgate, (bf16*)y, n_rows, H, V, V1, eps, floor_eps);
+                       ldgate, (bf16*)y, n_rows, H, V, V1, eps, floor_eps, q_scale);
     else
         esp_launch_pdl(ESP_PDL_SMALL, matrix_memory_finish_kernel<float>, dim3(blocks), dim3(256), 0, stream, o, m, w, gate,
-                       ldgate, (float*)y, n_rows, H, V, V1, eps, floor_eps);
+                       ldgate, (float*)y, n_rows, H, V, V1, eps, floor_eps, q_scale);
     return esp_launch_status();
 }
 
@@ -722,18 +798,21 @@ ESP_API int esp_conv_branches(const float* proj, const float* bias_y, const floa
     return esp_launch_status();
 }
 
-ESP_API int esp_diag_scan(const float* gates, const float* bias_r, const float* bias_i, const float* lam, float decay_scale,
+// gates: overwritten with the recurrence's coefficients.
+ESP_API int esp_diag_scan(float* gates, const float* bias_r, const float* bias_i, const float* lam, float decay_scale,
                           const float* u, const float* gate, float* state, long long state_stride, const int* seq_start,
-                          const int* seq_slot, void* out, int out_is_bf16, int n_seqs, int C, int blocks,
+                          const int* seq_slot, void* out, int out_is_bf16, int n_rows, int n_seqs, int C, int blocks,
                           cudaStream_t stream) {
-    if (n_seqs <= 0) return 0;
+    if (n_seqs <= 0 || n_rows <= 0) return 0;
     if (C <= 0 || blocks <= 0 || C % blocks != 0) return (int)cudaErrorInvalidValue;
-    dim3 grid(n_seqs, (C + 127) / 128);
+    esp_launch_pdl(ESP_PDL_SMALL, diag_coefficients_kernel, dim3(n_rows), dim3(C >= 1024 ? 256 : 128), 0, stream, gates, bias_r,
+                   bias_i, lam, decay_scale, u, C, C / blocks);
+    dim3 grid(n_seqs, (C + 31) / 32);
     if (out_is_bf16)
-        esp_launch_pdl(ESP_PDL_SMALL, diag_scan_kernel<bf16>, grid, dim3(128), 0, stream, gates, bias_r, bias_i, lam, decay_scale,
-                       u, gate, state, state_stride, seq_start, seq_slot, (bf16*)out, C, C / blocks);
+        esp_launch_pdl(ESP_PDL_SMALL, diag_scan_kernel<bf16>, grid, dim3(DIAG_THREADS), 0, stream, (const float*)gates, gate, state,
+                       state_stride, seq_start, seq_slot, (bf16*)out, C, C / blocks);
     else
-        esp_launch_pdl(ESP_PDL_SMALL, diag_scan_kernel<float>, grid, dim3(128), 0, stream, gates, bias_r, bias_i, lam, decay_scale,
-                       u, gate, state, state_stride, seq_start, seq_slot, (float*)out, C, C / blocks);
+        esp_launch_pdl(ESP_PDL_SMALL, diag_scan_kernel<float>, grid, dim3(DIAG_THREADS), 0, stream, (const float*)gates, gate, state,
+                       state_stride, seq_start, seq_slot, (float*)out, C, C / blocks);
     return esp_launch_status();
 }

@@ -245,20 +245,35 @@ class NormedAttention(Part):
     # -- which kernel a step of n token rows gets, and the index lists it needs ----------
     def kernel_for(self, n: int, page: int = PAGE) -> str:
         s = self.spec
-        if self.rt.dtype == torch.bfloat16 and page == PAGE and ops.attn_flash_fits(s.key_dim, s.value_dim):
-            return "flash"
+        if self.rt.dtype == torch.bfloat16 and page == PAGE:
+            same = s.key_dim == s.value_dim and s.scale > 0
+            if same and s.key_dim in (64, 128, 192, 256) and n <= DECODE_ROWS:
+                return "split"         # few rows: the keys are split over blocks
+            if same and ops.attn_prefill_tc05_fits(s.key_dim, page):
+                return "tc05"          # many rows: scores and weighted values in tensor memory
+            if ops.attn_flash_fits(s.key_dim, s.value_dim):
+                return "flash"         # keys and values of different sizes, any multiples of 8 up to 128
         return "plain"
 
     def step_arrays_key(self):
-        return ("attention_qknorm", self.rt.dtype, ops.attn_flash_fits(self.spec.key_dim, self.spec.value_dim))
+        s = self.spec
+        return ("attention_qknorm", self.rt.dtype, s.key_dim, s.value_dim, s.scale > 0)
 
     def step_arrays(self, step):
-        """Tiles of 64 new tokens for the tensor-core kernel: (sequence, first new token) per tile."""
-        if self.kernel_for(step.n_tokens) != "flash":
+        """Tiles of new tokens for the two tensor-core kernels of many rows: (sequence, first new token) per tile; for
+        the tensor-memory kernel the tiles that see the most keys come first (its blocks take them in order)."""
+        kind = self.kernel_for(step.n_tokens)
+        if kind == "tc05":
+            rows = ops.ATTN_TC05_TILE_ROWS
+            tiles = sorted(((i, f) for i, t in enumerate(step.news) for f in range(0, t, rows)),
+                           key=lambda sf: -(step.pasts[sf[0]] + min(sf[1] + rows, step.news[sf[0]])))
+        elif kind == "flash":
+            rows = 64
+            tiles = [(i, f) for i, t in enumerate(step.news) for f in range(0, t, rows)]
+        else:
             return {}
-        tiles = [(i, f) for i, t in enumerate(step.news) for f in range(0, t, 64)]
-        return {"attention.tiles64.seq": np.asarray([t[0] for t in tiles], dtype=np.int32),
-                "attention.tiles64.first": np.asarray([t[1] for t in tiles], dtype=np.int32)}
+        return {f"attention.tiles{rows}.seq": np.asarray([t[0] for t in tiles], dtype=np.int32),
+                f"attention.tiles{rows}.first": np.asarray([t[1] for t in tiles], dtype=np.int32)}
 
     def forward(self, h, ctx, layer):
         s, rt = self.spec, self.rt
@@ -273,8 +288,29 @@ class NormedAttention(Part):
                            s.num_heads, s.num_kv_heads, s.key_dim, s.value_dim, layer.writes, rt.status)
         o = rt.ws.get("attn_o", (n, self.o_width), rt.dtype)
         kind = self.kernel_for(n, layer.page)
-        tile_seq, tile_first = ctx.arrays.get("attention.tiles64.seq"), ctx.arrays.get("attention.tiles64.first")
-        if kind == "flash" and tile_seq is not None:
+        tile_seq = tile_first = None
+        if kind in ("tc05", "flash"):
+            rows = ops.ATTN_TC05_TILE_ROWS if kind == "tc05" else 64
+            tile_seq, tile_first = ctx.arrays.get(f"attention.tiles{rows}.seq"), ctx.arrays.get(f"attention.tiles{rows}.first")
+            if tile_seq is None:
+                kind = "plain"         # a step made without this part's lists
+        if kind == "split":
+            positions = table.shape[1] * layer.page
+            group = s.num_heads // s.num_kv_heads
+            kv_blocks = s.num_kv_heads * ((group + 15) // 16)
+            split = ops.attn_decode_split(n, kv_blocks, positions, s.key_dim, rt.sm_count)
+            n_splits = (positions + split - 1) // split
+            part_o = rt.ws.get("attn_part_o", (n, s.num_heads, n_splits, s.key_dim), torch.float32)
+            part_ml = rt.ws.get("attn_part_ml", (n, s.num_heads, n_splits, 2), torch.float32)
+            if getattr(rt, "attn_counters", None) is None:
+                rt.attn_counters = torch.zeros(ops.ATTN_DECODE_COUNTERS, dtype=torch.int32, device=rt.device)
+            ops.attn_decode(q, layer.k, layer.v, o, part_o, part_ml, rt.attn_counters, ctx.tok_seq, ctx.tok_pos, table, layer.page,
+                            s.num_heads, s.num_kv_heads, s.key_dim, s.window, split, n_splits, rt.status,
+                            seq_past=ctx.seq_past if layer.writes else None, scale=s.scale, sink=s.sink)
+        elif kind == "tc05":
+            ops.attn_prefill_tc05(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past, table, layer.page,
+                                  s.num_heads, s.num_kv_heads, s.key_dim, s.window, rt.status, scale=s.scale, sink=s.sink)
+        elif kind == "flash":
             ops.attn_prefill(q, layer.k, layer.v, o, tile_seq, tile_first, ctx.seq_start, ctx.seq_past, table, layer.page,
                              s.num_heads, s.num_kv_heads, s.key_dim, s.window, rt.status, vd=s.value_dim, scale=s.scale,
                              sink=s.sink)

@@ -7,7 +7,7 @@ import torch
 from ..csrc import ops
 from ..errors import Unsupported
 from .base import ParamSpec, Part, register
-from .linear import grouped_linear, grouped_swiglu_linear, grouped_uses_tc05, linear, swiglu_linear, xielu_linear
+from .linear import grouped_linear, grouped_swiglu_linear, grouped_uses_tc05, linear, relu2_linear, swiglu_linear, xielu_linear
 
 
 class DeferredMoeCombine:
@@ -284,10 +284,8 @@ class MoeSwiGluShared(Part):
 
 def _relu2_mlp(rt, h, w_up, w_down, out, tag):
     """out = down(relu(up h)^2)."""
-    z = rt.ws.get(tag + "_z", (h.shape[0], w_up.shape[0]), torch.float32)
-    linear(rt, h, w_up, z)
     act = rt.ws.get(tag + "_act", (h.shape[0], w_up.shape[0]), rt.dtype)
-    ops.relu2(z, act)
+    relu2_linear(rt, h, w_up, act, tag)
     linear(rt, act, w_down, out)
     return out
 
@@ -401,8 +399,9 @@ class ScaledInputMoe(Part):
             ops.gemm_tc05(act, self.w_down, out, rt.status, tiles=tiles)
         elif h.dtype == torch.bfloat16 and self.w_up.dtype == torch.bfloat16 and self.w_down.dtype == torch.bfloat16 \
                 and ops.skinny_fits(H) and ops.skinny_fits(Im):
-            ops.gemm_skinny(h, self.w_up, z, a_rows=perm_token, row_scale=perm_weight, group_offsets=offsets, rows=rows, max_rows=n)
-            ops.relu2(z, act)
+            # the weight and the activation are the first product's epilogue
+            ops.gemm_skinny(h, self.w_up, act, a_rows=perm_token, row_scale=perm_weight, group_offsets=offsets, rows=rows,
+                            max_rows=n, relu2=True)
             ops.gemm_skinny(act, self.w_down, out, group_offsets=offsets, rows=rows, max_rows=n)
         else:
             ops.gemm_simt(h, self.w_up, z, a_rows=perm_token, row_scale=perm_weight, group_offsets=offsets, rows=rows)

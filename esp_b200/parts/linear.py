@@ -77,6 +77,18 @@ def xielu_linear(rt, a, w, pq, act, tag):
     return act
 
 
+def relu2_linear(rt, a, w, act, tag):
+    """act = max(a @ w.T, 0)^2 in the activation dtype.  Few rows: the activation is the weight-streaming product's
+    epilogue; else the product, then the activation's own kernel."""
+    if _both_bf16(a, w) and a.shape[0] <= SKINNY_ROWS and ops.skinny_fits(a.shape[1]):
+        ops.gemm_skinny(a, w, act, relu2=True)
+        return act
+    z = rt.ws.get(tag + "_z", (a.shape[0], w.shape[0]), torch.float32)
+    linear(rt, a, w, z)
+    ops.relu2(z, act)
+    return act
+
+
 def grouped_uses_tc05(a, w, rows, max_rows=None) -> bool:
     """Whether a grouped product of ``rows`` (token, expert) rows, at most ``max_rows`` of them in one group,
     runs on TMA + tcgen05.  The weight-streaming kernel keeps a group's rows in one or two blocks of eight; with

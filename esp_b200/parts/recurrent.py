@@ -194,8 +194,9 @@ class DecayBonusRecurrence(Part):
 class MatrixMemory(Part):
     """Matrix memory with exponential gating (see ``MatrixMemorySpec``).  One packed product makes q, k, v, the output
     gate and the two gate scalars per head; a short kernel turns the scalars into the running maximum m, the decay
-    exp(f + m' - m) and the input weight exp(i - m) (32-bit, a chain over the tokens) and lays out what the shared
-    recurrence kernel reads; the normaliser n rides along as one more value column whose value is always one.  Per
+    exp(f + m' - m) and the input weight exp(i - m) (32-bit, a chain over the tokens); the shared recurrence kernel
+    takes the decay as one number per head and token and the input weight as a factor on the values; the normaliser n
+    rides along as one more value column whose value is always one.  Per
     slot the state holds S and n as [heads, value columns, key channels] floats and then m per head."""
 
     graph_safe = True
@@ -256,18 +257,18 @@ class MatrixMemory(Part):
         proj = rt.ws.get("mm_proj", (n, self.proj_width), torch.float32)
         linear(rt, h, self.w_in, proj)
         part = lambda t: proj[:, self.cols_at[t][0]:self.cols_at[t][1]]
-        qkd = rt.ws.get("rec_gates", (3, n, self.kw), torch.float32)
         v1 = rt.ws.get("mm_values", (n, H * self.cols), torch.float32)
-        m = rt.ws.get("mm_max", (n, H), torch.float32)
-        ops.matrix_memory_prepare(part("q"), part("k"), part("v"), part("input_gate"), part("forget_gate"), self.proj_width,
-                                  self.gate_bias[0], self.gate_bias[1], s.gate_cap, s.key_dim ** -0.5,
-                                  layer.state[:, self.state_words:], ctx.seq_start, ctx.seq_slot, qkd[0], qkd[1], qkd[2], v1, m,
-                                  ctx.n_seqs, H, s.key_dim, s.value_dim, self.cols)
+        ktm = rt.ws.get("mm_keep_take_max", (3, n, H), torch.float32)
+        ops.matrix_memory_prepare(part("v"), part("input_gate"), part("forget_gate"), self.proj_width, self.gate_bias[0],
+                                  self.gate_bias[1], s.gate_cap, layer.state[:, self.state_words:], ctx.seq_start, ctx.seq_slot,
+                                  v1, ktm, ctx.n_seqs, H, s.value_dim, self.cols)
         o = rt.ws.get("rec_out", (n, H * self.cols), torch.float32)
-        ops.gated_scan(ops.SCAN_LOWER_SIGMOID, qkd[0], qkd[1], qkd[2], v1, None, None, None, layer.state, ctx.seq_start,
+        # queries and keys go in as projected: the input weight rides on the values, the queries' scale on the result
+        ops.gated_scan(ops.SCAN_SCALAR_DECAY, part("q"), part("k"), ktm[0], v1, None, None, None, layer.state, ctx.seq_start,
                        ctx.seq_slot, o, ctx.n_seqs, H, s.key_dim, self.cols, ready=True)
         y = rt.ws.get("rec_normed", (n, self.vw), rt.dtype)
-        ops.matrix_memory_finish(o, m, self.norm_w, part("gate"), y, H, s.value_dim, self.cols, s.eps, self.FLOOR)
+        ops.matrix_memory_finish(o, ktm[2], self.norm_w, part("gate"), y, H, s.value_dim, self.cols, s.eps, self.FLOOR,
+                                 q_scale=s.key_dim ** -0.5)
         out = rt.ws.get("mixer_out", (n, s.hidden), torch.float32)
         linear(rt, y, self.w_o, out)
         return out

@@ -37,6 +37,8 @@ ALONE = {
                                                  "q_temp": {"coef": 0.6, "every": 5}}, "mlp": None},
     "attention_plain_kernel": {"type": "attention", "mixer": {"heads": 3, "kv_heads": 3, "dim": 12, "vdim": 20, "scale": 0.4},
                                "mlp": None},
+    "attention_equal_sizes": {"type": "attention", "mixer": {"heads": 2, "kv_heads": 1, "dim": 64, "vdim": 64, "scale": 0.11,
+                                                             "q_temp": {"coef": 0.3, "every": 64}}, "mlp": None},
     "mlstm": {"type": "mlstm", "mixer": {"heads": 2, "dim": 24, "vdim": 40, "gate_cap": 10.0}, "mlp": None},
     "rglru": {"type": "rglru", "mixer": {"width": 48, "blocks": 2, "conv": 3}, "mlp": None},
     "dense": {"type": "rglru", "mixer": {"width": 16, "blocks": 1, "conv": 2}, "mlp": {"kind": "dense", "ff": 72}},

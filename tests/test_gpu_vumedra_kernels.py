@@ -33,12 +33,44 @@ def paged(rows, table, n_pages, dtype):
 
 
 # ------------------------------------------------------------------------------------------------ attention
-@pytest.mark.parametrize("kernel", ["plain32", "plain16", "tensor16"])
-@pytest.mark.parametrize("H, G, K, V", [(4, 2, 16, 40), (3, 1, 64, 80), (1, 1, 24, 8), (2, 2, 128, 128)])
+def run_attention(kernel, q, k_pool, v_pool, out, table, first, new, H, G, K, V, scale, status):
+    """The new tokens are positions first .. first + new - 1 of one sequence whose pages ``table`` lists."""
+    args = (q, k_pool, v_pool, out)
+    tables = i32([table])
+    if kernel == "tensor16":              # mma.sync, tiles of 64 rows
+        firsts = list(range(0, new, 64))
+        ops.attn_prefill(*args, i32([0] * len(firsts)), i32(firsts), i32([0, new]), i32([first]), tables, PAGE, H, G, K, None,
+                         status, vd=V, scale=scale, sink=True)
+    elif kernel == "tmem16":              # tcgen05, tiles of 128 rows
+        firsts = list(range(0, new, ops.ATTN_TC05_TILE_ROWS))
+        ops.attn_prefill_tc05(*args, i32([0] * len(firsts)), i32(firsts), i32([0, new]), i32([first]), tables, PAGE, H, G, K,
+                              None, status, scale=scale, sink=True)
+    elif kernel == "split16":             # keys split over blocks, for few rows
+        split = 128
+        n_splits = (len(table) * PAGE + split - 1) // split
+        part_o = torch.zeros(new, H, n_splits, K, device=DEV)
+        part_ml = torch.zeros(new, H, n_splits, 2, device=DEV)
+        counters = torch.zeros(ops.ATTN_DECODE_COUNTERS, dtype=torch.int32, device=DEV)
+        ops.attn_decode(*args, part_o, part_ml, counters, i32([0] * new), i32(list(range(first, first + new))), tables, PAGE, H, G,
+                        K, None, split, n_splits, status, scale=scale, sink=True)
+        assert int(counters.abs().sum().item()) == 0
+    else:
+        ops.attn_simt(*args, i32([0] * new), i32(list(range(first, first + new))), tables, PAGE, H, G, K, None, status, vd=V,
+                      scale=scale, sink=True)
+
+
+def takes(kernel, K, V):
+    return kernel in ("plain32", "plain16", "tensor16") or (K == V and K in (64, 128))
+
+
+@pytest.mark.parametrize("kernel", ["plain32", "plain16", "tensor16", "tmem16", "split16"])
+@pytest.mark.parametrize("H, G, K, V", [(4, 2, 16, 40), (3, 1, 64, 80), (1, 1, 24, 8), (2, 2, 128, 128), (8, 2, 64, 64)])
 def test_attention_finds_one_key_wherever_it_lies(kernel, H, G, K, V):
     """700 cached positions in pages handed out in no order; the new tokens are the last 70.  For every probed place
     (far back, both sides of page borders, the query itself, the first position) one key gets a large score for
     one query head, so that head's output must be that position's value row."""
+    if not takes(kernel, K, V):
+        pytest.skip("this kernel wants keys and values of one size, 64 or 128")
     dtype = torch.float32 if kernel == "plain32" else torch.bfloat16
     g = torch.Generator().manual_seed(5)
     T, new = 700, 70
@@ -61,32 +93,30 @@ def test_attention_finds_one_key_wherever_it_lies(kernel, H, G, K, V):
     n_pages = 16
     table = [7, 2, 11, 0, 5, 13, 1, 9, 3, 15, 4]
     out = torch.zeros(new, H * V, dtype=dtype, device=DEV)
-    args = (dev(q.reshape(new, H * K), dtype), dev(paged(k, table, n_pages, dtype)), dev(paged(v, table, n_pages, dtype)), out)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    if kernel == "tensor16":
-        ops.attn_prefill(*args, i32([0, 0]), i32([0, 64]), i32([0, new]), i32([T - new]), i32([table]), PAGE, H, G, K, None,
-                         status, vd=V, scale=scale, sink=True)
-    else:
-        ops.attn_simt(*args, i32([0] * new), i32(list(range(T - new, T))), i32([table]), PAGE, H, G, K, None, status, vd=V,
-                      scale=scale, sink=True)
+    run_attention(kernel, dev(q.reshape(new, H * K), dtype), dev(paged(k, table, n_pages, dtype)),
+                  dev(paged(v, table, n_pages, dtype)), out, table, T - new, new, H, G, K, V, scale, status)
     assert int(status.item()) == 0
     err = (out.double().cpu().view(new, H, V) - want).abs().max().item()
     assert err < (1e-5 if dtype == torch.float32 else 5e-2), err
 
 
-@pytest.mark.parametrize("kernel", ["plain32", "tensor16"])
-def test_the_sink_takes_the_weight_that_no_key_earns(kernel):
+@pytest.mark.parametrize("K, V", [(32, 16), (64, 64)])
+@pytest.mark.parametrize("kernel", ["plain32", "tensor16", "tmem16", "split16"])
+def test_the_sink_takes_the_weight_that_no_key_earns(kernel, K, V):
     """Scores far below zero: with the extra term in the denominator the output is nearly nothing, without it the
     plain average of the values; scores far above zero: the sink does not matter."""
+    if not takes(kernel, K, V):
+        pytest.skip("this kernel wants keys and values of one size, 64 or 128")
     dtype = torch.float32 if kernel == "plain32" else torch.bfloat16
-    H, K, V, T = 2, 32, 16, 130
+    H, T = 2, 120 if kernel == "split16" else 130
     g = torch.Generator().manual_seed(8)
     direction = torch.randn(K, generator=g)
     direction /= direction.norm()
     q = (direction * 4).repeat(T, H, 1)
     q[:, 1] *= -1                                    # head 0: every score is -16 * scale; head 1: +16 * scale
     k = (-direction * 4).repeat(T, 1, 1)
-    v = torch.randn(T, 1, V, generator=g) + 3.0
+    v = torch.randn(T, 1, V, generator=g) * 0.3 + 3.0
     q, k, v = (t.to(dtype).double() for t in (q, k, v))
     pos = torch.arange(T)
     want = plain.attend_with_sink(q, k, v, 1.0, pos, pos)
@@ -95,13 +125,9 @@ def test_the_sink_takes_the_weight_that_no_key_earns(kernel):
     table = [2, 0, 1]
     out = torch.zeros(T, H * V, dtype=dtype, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    args = (dev(q.reshape(T, H * K), dtype), dev(paged(k, table, 3, dtype)), dev(paged(v, table, 3, dtype)), out)
-    if kernel == "tensor16":
-        ops.attn_prefill(*args, i32([0, 0, 0]), i32([0, 64, 128]), i32([0, T]), i32([0]), i32([table]), PAGE, H, 1, K, None,
-                         status, vd=V, scale=1.0, sink=True)
-    else:
-        ops.attn_simt(*args, i32([0] * T), i32(list(range(T))), i32([table]), PAGE, H, 1, K, None, status, vd=V, scale=1.0,
-                      sink=True)
+    run_attention(kernel, dev(q.reshape(T, H * K), dtype), dev(paged(k, table, 3, dtype)), dev(paged(v, table, 3, dtype)), out,
+                  table, 0, T, H, 1, K, V, 1.0, status)
+    assert int(status.item()) == 0
     got = out.double().cpu().view(T, H, V)
     assert (got - want).abs().max() < (1e-5 if dtype == torch.float32 else 3e-2)
 
@@ -206,12 +232,14 @@ def test_squared_relu_with_a_factor_per_row():
 # ------------------------------------------------------------------------------------------------ recurrences
 def test_matrix_memory_gates_follow_the_running_maximum():
     """Input gates that jump far above and forget gates that fall far below what came before, over two runs of one
-    sequence and a second sequence in another slot: keep, take and m against the chain written out."""
+    sequence and a second sequence in another slot: decay, input weight and m against the chain written out, and the
+    value rows with their weight and the column of the normaliser."""
     g = torch.Generator().manual_seed(9)
-    H, K, V, cap = 2, 8, 4, 7.0
+    H, V, cap = 2, 4, 7.0
     cols = 8
     runs = [[5, 3], [2, 4]]                              # step 1: 5 tokens of sequence a, 3 of b; step 2: 2 and 4
-    ld = 2 * H * K + H * V + 2 * H
+    ld = H * V + 2 * H
+    bias = torch.randn(2, H, generator=g)
     m_state = torch.zeros(4, H, device=DEV)
     total = {0: [], 1: []}
     outs = {0: [], 1: []}
@@ -219,41 +247,69 @@ def test_matrix_memory_gates_follow_the_running_maximum():
         n = sum(run)
         proj = torch.randn(n, ld, generator=g)
         proj[:, -2 * H:] *= 6                            # raw gates far out, so that the cap and the maximum both act
-        bias = torch.randn(2, H, generator=g)
-        if not total[0]:
-            first_bias = bias
-        bias = first_bias
         pd = dev(proj)
         starts = np.cumsum([0] + run).tolist()
-        at = np.cumsum([0, H * K, H * K, H * V, H]).tolist()
-        q, k, v, gi, gf = (pd[:, a:b] for a, b in zip(at, at[1:] + [ld]))
-        qo, ko, do = (torch.zeros(n, H * K, device=DEV) for _ in range(3))
-        vo, mo = torch.zeros(n, H * cols, device=DEV), torch.zeros(n, H, device=DEV)
-        ops.matrix_memory_prepare(q, k, v, gi, gf, ld, dev(bias[0]), dev(bias[1]), cap, 0.5, m_state[1:], i32(starts), i32([2, 0]),
-                                  qo, ko, do, vo, mo, 2, H, K, V, cols)
+        v, gi, gf = pd[:, :H * V], pd[:, H * V:H * V + H], pd[:, H * V + H:]
+        vo, ktm = torch.zeros(n, H * cols, device=DEV), torch.zeros(3, n, H, device=DEV)
+        ops.matrix_memory_prepare(v, gi, gf, ld, dev(bias[0]), dev(bias[1]), cap, m_state[1:], i32(starts), i32([2, 0]), vo, ktm,
+                                  2, H, V, cols)
         for s in (0, 1):
             sl = slice(starts[s], starts[s + 1])
             total[s].append(proj[sl])
-            outs[s].append(tuple(t[sl].cpu() for t in (qo, ko, do, vo, mo)))
+            outs[s].append((vo[sl].cpu(), ktm[0, sl].cpu(), ktm[1, sl].cpu(), ktm[2, sl].cpu()))
     for s in (0, 1):
         proj = torch.cat(total[s]).double()
-        qo, ko, do, vo, mo = (torch.cat([o[i] for o in outs[s]]).double() for i in range(5))
-        gi = cap * torch.tanh((proj[:, -2 * H:-H] + first_bias[0].double()) / cap)
-        gf = plain.logsigmoid(cap * torch.tanh((proj[:, -H:] + first_bias[1].double()) / cap))
+        vo, keep_o, take_o, mo = (torch.cat([o[i] for o in outs[s]]).double() for i in range(4))
+        gi = cap * torch.tanh((proj[:, -2 * H:-H] + bias[0].double()) / cap)
+        gf = plain.logsigmoid(cap * torch.tanh((proj[:, -H:] + bias[1].double()) / cap))
         m = torch.zeros(H, dtype=torch.float64)
         for t in range(proj.shape[0]):
             m_new = torch.maximum(gf[t] + m, gi[t])
             keep, take = torch.exp(gf[t] + m - m_new), torch.exp(gi[t] - m_new)
             m = m_new
-            assert torch.allclose(mo[t], m, atol=1e-5)
-            assert torch.allclose(do[t].view(H, K), keep[:, None].expand(H, K), atol=1e-5)
-            assert torch.allclose(ko[t].view(H, K), take[:, None] * proj[t, H * K:2 * H * K].view(H, K), atol=1e-5)
-            assert torch.allclose(qo[t], proj[t, :H * K] * 0.5, atol=1e-6)
+            assert torch.allclose(mo[t], m, atol=1e-5) and torch.allclose(keep_o[t], keep, atol=1e-5)
+            assert torch.allclose(take_o[t], take, atol=1e-5)
             vr = vo[t].view(H, cols)
-            assert torch.allclose(vr[:, :V], proj[t, 2 * H * K:2 * H * K + H * V].view(H, V), atol=1e-6)
-            assert torch.equal(vr[:, V], torch.ones(H, dtype=torch.float64)) and float(vr[:, V + 1:].abs().max()) == 0
-    assert torch.allclose(m_state[3].cpu().double(), torch.cat([o[4] for o in outs[0]])[-1].double(), atol=1e-6)
+            assert torch.allclose(vr[:, :V], take[:, None] * proj[t, :H * V].view(H, V), atol=1e-5)
+            assert torch.allclose(vr[:, V], take, atol=1e-5) and float(vr[:, V + 1:].abs().max()) == 0
+    assert torch.allclose(m_state[3].cpu().double(), torch.cat([o[3] for o in outs[0]])[-1].double(), atol=1e-6)
     assert float(m_state[0].abs().max()) == 0 and float(m_state[2].abs().max()) == 0
+
+
+def test_recurrence_with_one_decay_per_head_and_the_normalised_readout():
+    """The shared recurrence with a ready-made decay per head and token, from a state left by an earlier call, and
+    what follows it: quotient by max(|n . q|, exp(-m)), unit root mean square per head, weight and sigmoid gate."""
+    g = torch.Generator().manual_seed(10)
+    H, K, V, cols, n = 3, 24, 6, 8, 21
+    q, k = torch.randn(n, H * K, generator=g), torch.randn(n, H * K, generator=g)
+    v = torch.zeros(n, H, cols)
+    v[:, :, :V] = torch.randn(n, H, V, generator=g)
+    v[:, :, V] = 1.0
+    take = torch.rand(n, H, generator=g) + 0.2
+    v = v * take[:, :, None]
+    keep = torch.rand(n, H, generator=g)
+    m = torch.randn(n, H, generator=g)
+    state = torch.zeros(3, H * cols * K, device=DEV)
+    out = []
+    for a, b in ((0, 8), (8, 21)):                      # two calls: the second goes on from the first's state
+        o = torch.zeros(b - a, H * cols, device=DEV)
+        ops.gated_scan(ops.SCAN_SCALAR_DECAY, dev(q[a:b]), dev(k[a:b]), dev(keep[a:b]), dev(v[a:b].reshape(b - a, -1)), None, None,
+                       None, state, i32([0, b - a]), i32([1]), o, 1, H, K, cols, ready=True)
+        out.append(o)
+    o = torch.cat(out)
+    S = torch.zeros(H, K, cols, dtype=torch.float64)
+    want = torch.zeros(n, H, cols, dtype=torch.float64)
+    for t in range(n):
+        S = keep[t].double()[:, None, None] * S + k[t].double().view(H, K)[:, :, None] * v[t].double()[:, None, :]
+        want[t] = torch.einsum("hkc,hk->hc", S, q[t].double().view(H, K))
+    assert (o.double().cpu().view(n, H, cols) - want).abs().max() < 1e-4
+    assert float(state[[0, 2]].abs().max()) == 0
+    w, gate, qs, eps = torch.rand(H * V, generator=g) + 0.5, torch.randn(n, H * V, generator=g), K ** -0.5, 1e-5
+    y = torch.zeros(n, H * V, device=DEV)
+    ops.matrix_memory_finish(o, dev(m), dev(w), dev(gate), y, H, V, cols, eps, 1e-6, q_scale=qs)
+    den = torch.maximum((want[:, :, V] * qs).abs(), torch.exp(-m.double())) + 1e-6
+    val = plain.rms(want[:, :, :V] * qs / den[:, :, None], eps).reshape(n, H * V) * w.double() * torch.sigmoid(gate.double())
+    assert (y.double().cpu() - val).abs().max() < 1e-4
 
 
 def test_convolution_state_shorter_than_its_reach_and_the_diagonal_recurrence():
