@@ -486,7 +486,7 @@ def vumedra_config(width, ff, layers, vocab):
     out = [{"type": pattern[i % 4]["type"], "mixer": dict(pattern[i % 4]["mixer"]),
             "mlp": dict(moe) if i % 2 else {"kind": "dense", "ff": ff}} for i in range(layers)]
     return {"architecture": "Vumedra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": out}
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 17}}, "layers": out}
 
 
 def sparse_qwen2_config(width, ff, layers, vocab):
