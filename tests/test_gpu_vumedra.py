@@ -44,12 +44,19 @@ ALONE = {
     "dense": {"type": "rglru", "mixer": {"width": 16, "blocks": 1, "conv": 2}, "mlp": {"kind": "dense", "ff": 72}},
     "moe": {"type": "rglru", "mixer": {"width": 16, "blocks": 1, "conv": 2},
             "mlp": {"kind": "moe", "router": {"experts": 7, "top": 2}, "expert": {"ff": 24}, "shared": {"ff": 40}}},
+    # a width of 128 and experts of 32: long steps take the router's tensor-core logits and the grouped TMA + tcgen05 products
+    "moe_wide": {"type": "rglru", "mixer": {"width": 32, "blocks": 2, "conv": 2}, "width": 128,
+                 "mlp": {"kind": "moe", "router": {"experts": 4, "top": 2}, "expert": {"ff": 32}, "shared": {"ff": 16}}},
 }
 
 
 @functools.lru_cache(maxsize=None)
 def model(name, seed=7):
-    raw = one_layer(ALONE[name]) if name in ALONE else case(name)
+    if name in ALONE:
+        layer = dict(ALONE[name])
+        raw = one_layer(layer, width=layer.pop("width", 64))
+    else:
+        raw = case(name)
     stored = random_weights(raw, seed)
     return raw, stored, {k: v.double() for k, v in stored.items()}
 
