@@ -178,6 +178,9 @@ class VumedraConfig:
         return ModelPlan(architecture=ARCHITECTURE, hidden=self.width, vocab=self.vocab, max_positions=POSITION_BOUND,
                          blocks=blocks, schedule=schedule, final_norm=norm("final.norm"), embed_weight="embed",
                          head_weight="head",
+                         # a layer without feed-forward has no second pair of norms; a checkpoint that stores them all
+                         # the same is read without them
+                         tolerated_suffixes=(".norm2", ".norm2b"),
                          embedding=SummedEmbeddingSpec(self.width, HashedBigramSpec(b["buckets"], b["mul_prev"], b["mul_cur"],
                                                                                     "bigram"), SINUSOID_BASE))
 

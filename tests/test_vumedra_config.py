@@ -79,6 +79,34 @@ def test_refusals(change, error):
         config_from_dict(raw)
 
 
+def test_norms_of_a_missing_feed_forward_may_be_stored():
+    from esp_b200.weights.loader import check_names_and_shapes
+
+    class Names:
+        def __init__(self, shapes):
+            self.shapes = shapes
+
+        def names(self):
+            return list(self.shapes)
+
+        def shape(self, n):
+            return self.shapes[n]
+
+        def dtype(self, n):
+            return torch.bfloat16
+
+    raw = case("A")
+    cfg = config_from_dict(raw)
+    specs = parameter_specs(cfg)
+    shapes = dict(plain.tensor_shapes(raw))
+    shapes.update({"l2.norm2": (), "l2.norm2b": ()})          # layer 2 has no feed-forward
+    check_names_and_shapes(specs, Names(shapes), cfg.plan().tolerated_suffixes)
+    shapes["l2.norm3"] = ()
+    from esp_b200.errors import InvalidWeights
+    with pytest.raises(InvalidWeights):
+        check_names_and_shapes(specs, Names(shapes), cfg.plan().tolerated_suffixes)
+
+
 def test_random_model_folder_round_trips(tmp_path):
     cfg = config_from_dict(case("B"))
     write_model_folder(cfg, 5, tmp_path)
